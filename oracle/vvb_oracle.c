@@ -1,0 +1,279 @@
+/*
+ * vvb_oracle.c -- CPU restatement of the reference's per-token layer kernels.
+ *
+ * TEST INFRASTRUCTURE ONLY. Nothing in the shipped library links, loads or
+ * calls this file; it exists so the CUDA kernels can be checked against the
+ * arithmetic the reference's CPU path performs. Parity is pinned: this file is
+ * checked bit-for-bit against the reference's own compiled CPU kernels
+ * (oracle/_ref/libvvref_cpu.so, built by oracle/Makefile from the reference's
+ * src/cpu/cpu_kernels.c) and against fixtures that build produced
+ * (tests/golden/, written by tests/golden/make_golden.py).
+ *
+ * Activations are FP32 and weights FP16, as on the reference's CPU path
+ * (include/vibevoice/cpu_kernels.h:5-7). Each function names the reference
+ * lines whose arithmetic it follows. The loops are arranged differently from
+ * the reference (trigonometry hoisted out of the head loop, explicit row
+ * blocking) but every floating-point operation that reaches a result is the
+ * same operation on the same operands in the same order, so results are
+ * bit-identical.
+ *
+ * Build: gcc -O2 -std=c11 -fopenmp -fPIC -shared (no -ffast-math, no -mfma:
+ * a fused multiply-add would change the RoPE and SwiGLU roundings).
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define ORC_OK 0
+#define ORC_ERR_INVALID_ARG (-1) /* include/vibevoice/types.h:22 */
+#define ORC_ERR_NULL_PTR (-2)    /* include/vibevoice/types.h:23 */
+
+/* IEEE binary16 -> binary32, exact (include/vibevoice/types.h:107-129). */
+float orc_half_to_float(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    const uint32_t e = (h >> 10) & 0x1Fu;
+    uint32_t m = h & 0x3FFu;
+    uint32_t bits;
+    if (e == 31u) {
+        bits = sign | 0x7F800000u | (m << 13);
+    } else if (e != 0u) {
+        bits = sign | ((e + 112u) << 23) | (m << 13);
+    } else if (m == 0u) {
+        bits = sign;
+    } else {
+        /* subnormal: value = m * 2^-24; normalise the mantissa */
+        uint32_t ex = 113u;
+        do { m <<= 1; ex--; } while (!(m & 0x400u));
+        bits = sign | (ex << 23) | ((m & 0x3FFu) << 13);
+    }
+    float f;
+    memcpy(&f, &bits, sizeof f);
+    return f;
+}
+
+/* binary32 -> binary16, round to nearest even: the rounding CUDA's
+ * __float2half and torch's .half() perform (include/vibevoice/types.h:171-196). */
+uint16_t orc_float_to_half_rne(float f) {
+    uint32_t u;
+    memcpy(&u, &f, sizeof u);
+    const uint16_t sign = (uint16_t)((u >> 16) & 0x8000u);
+    const uint32_t a = u & 0x7FFFFFFFu;
+    if (a > 0x7F800000u) return (uint16_t)(sign | 0x7E00u);       /* NaN */
+    if (a >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u);      /* inf / overflow */
+    if (a >= 0x38800000u) {                                       /* normal */
+        uint32_t h = (a >> 13) - (112u << 10);
+        const uint32_t rest = a & 0x1FFFu;
+        h += (rest > 0x1000u) || (rest == 0x1000u && (h & 1u));
+        return (uint16_t)(sign | h);
+    }
+    if (a <= 0x33000000u) return sign;                            /* <= 2^-25 */
+    const uint32_t shift = 126u - (a >> 23);                      /* 14..24 */
+    const uint32_t m = (a & 0x7FFFFFu) | 0x800000u;
+    uint32_t h = m >> shift;
+    const uint32_t rest = m & ((1u << shift) - 1u);
+    const uint32_t halfway = 1u << (shift - 1u);
+    h += (rest > halfway) || (rest == halfway && (h & 1u));
+    return (uint16_t)(sign | h);
+}
+
+void orc_widen_f16(const uint16_t* src, float* dst, size_t n) {
+    ptrdiff_t i;
+#pragma omp parallel for schedule(static)
+    for (i = 0; i < (ptrdiff_t)n; i++) dst[i] = orc_half_to_float(src[i]);
+}
+
+void orc_round_f16(const float* src, uint16_t* dst, size_t n) {
+    ptrdiff_t i;
+#pragma omp parallel for schedule(static)
+    for (i = 0; i < (ptrdiff_t)n; i++) dst[i] = orc_float_to_half_rne(src[i]);
+}
+
+/* RMSNorm, src/cpu/cpu_kernels.c:1432-1451: sum of squares in double,
+ * inv = 1/sqrtf((float)(ss/n) + eps) in float, y = (x*inv)*w. */
+int orc_rmsnorm(const float* in, const uint16_t* w_f16, float* out,
+                int rows, int n, float eps) {
+    if (!in || !w_f16 || !out) return ORC_ERR_NULL_PTR;
+    if (rows < 0 || n <= 0) return ORC_ERR_INVALID_ARG;
+    float* w = (float*)malloc(sizeof(float) * (size_t)n);
+    if (!w) return ORC_ERR_INVALID_ARG;
+    for (int i = 0; i < n; i++) w[i] = orc_half_to_float(w_f16[i]);
+    int r;
+#pragma omp parallel for schedule(static)
+    for (r = 0; r < rows; r++) {
+        const float* x = in + (size_t)r * (size_t)n;
+        float* y = out + (size_t)r * (size_t)n;
+        double acc = 0.0;
+        for (int i = 0; i < n; i++) acc += (double)x[i] * x[i];
+        const float mean = (float)(acc / n);
+        const float inv = 1.0f / sqrtf(mean + eps);
+        for (int i = 0; i < n; i++) {
+            const float scaled = x[i] * inv;
+            y[i] = scaled * w[i];
+        }
+    }
+    free(w);
+    return ORC_OK;
+}
+
+/* RoPE, src/cpu/cpu_kernels.c:1453-1478: freq_i = powf(theta, -2i/hd),
+ * ang = (float)pos * freq_i, pairs (i, i + hd/2):
+ *   v[i] = a*c - b*s ; v[i+hd/2] = a*s + b*c   (four products, each rounded).
+ * cos/sin depend only on (pos, i), so they are computed once per row. */
+int orc_rope(float* x, int rows, int n_heads, int head_dim,
+             int position_offset, float theta) {
+    if (!x) return ORC_ERR_NULL_PTR;
+    if (rows < 0 || n_heads < 0 || head_dim < 0) return ORC_ERR_INVALID_ARG;
+    const int half = head_dim / 2;
+    if (half == 0) return ORC_OK;
+    float* freq = (float*)malloc(sizeof(float) * (size_t)half);
+    if (!freq) return ORC_ERR_INVALID_ARG;
+    for (int i = 0; i < half; i++)
+        freq[i] = powf(theta, -2.0f * (float)i / (float)head_dim);
+    int r;
+#pragma omp parallel
+    {
+        float* cs = (float*)malloc(sizeof(float) * 2u * (size_t)half);
+#pragma omp for schedule(static)
+        for (r = 0; r < rows; r++) {
+            const float pos = (float)(position_offset + r);
+            for (int i = 0; i < half; i++) {
+                const float ang = pos * freq[i];
+                cs[i] = cosf(ang);
+                cs[half + i] = sinf(ang);
+            }
+            for (int h = 0; h < n_heads; h++) {
+                float* v = x + ((size_t)r * (size_t)n_heads + (size_t)h) * (size_t)head_dim;
+                for (int i = 0; i < half; i++) {
+                    const float c = cs[i], s = cs[half + i];
+                    const float a = v[i], b = v[i + half];
+                    const float ac = a * c, bs = b * s;
+                    const float as = a * s, bc = b * c;
+                    v[i] = ac - bs;
+                    v[i + half] = as + bc;
+                }
+            }
+        }
+        free(cs);
+    }
+    free(freq);
+    return ORC_OK;
+}
+
+/* The 64 (head_dim/2) inverse frequencies exactly as the reference's CPU
+ * kernel forms them (cpu_kernels.c:1468), for tests that need the table. */
+int orc_rope_inv_freq(float* out, int head_dim, float theta) {
+    if (!out) return ORC_ERR_NULL_PTR;
+    for (int i = 0; i < head_dim / 2; i++)
+        out[i] = powf(theta, -2.0f * (float)i / (float)head_dim);
+    return ORC_OK;
+}
+
+/* SwiGLU, src/cpu/cpu_kernels.c:1536-1548: (g / (1 + expf(-g))) * up. */
+int orc_swiglu(const float* gate, const float* up, float* out, size_t n) {
+    if (!gate || !up || !out) return ORC_ERR_NULL_PTR;
+    ptrdiff_t i;
+#pragma omp parallel for schedule(static)
+    for (i = 0; i < (ptrdiff_t)n; i++) {
+        const float g = gate[i];
+        const float den = 1.0f + expf(-g);
+        const float act = g / den;
+        out[i] = act * up[i];
+    }
+    return ORC_OK;
+}
+
+/* Residual add, src/cpu/cpu_kernels.c:1550-1558: x += y in float. */
+int orc_residual_add(float* x, const float* y, size_t n) {
+    if (!x || !y) return ORC_ERR_NULL_PTR;
+    ptrdiff_t i;
+#pragma omp parallel for schedule(static)
+    for (i = 0; i < (ptrdiff_t)n; i++) x[i] = x[i] + y[i];
+    return ORC_OK;
+}
+
+/* Embedding gather, src/cpu/cpu_kernels.c:1560-1568: row ids[r] of the FP16
+ * table, widened exactly to float. */
+int orc_embedding(const uint16_t* table, const int32_t* ids, float* out,
+                  int rows, int hidden) {
+    if (!table || !ids || !out) return ORC_ERR_NULL_PTR;
+    int r;
+#pragma omp parallel for schedule(static)
+    for (r = 0; r < rows; r++) {
+        const uint16_t* src = table + (size_t)ids[r] * (size_t)hidden;
+        float* dst = out + (size_t)r * (size_t)hidden;
+        for (int i = 0; i < hidden; i++) dst[i] = orc_half_to_float(src[i]);
+    }
+    return ORC_OK;
+}
+
+/* ---- FP16-boundary composites: what the engine's FP16 buffers would hold
+ * if each reference CPU op ran on the widened values and its result were
+ * rounded back to FP16 (the device stores FP16: src/cuda/conv_vae.cu:29-31,
+ * src/cuda/rmsnorm.cu:61). ---- */
+
+/* hidden' = f16(hidden + delta); normed = f16(rmsnorm(widen(hidden'))).
+ * Mirrors vv_residual_add_dev followed by vv_rmsnorm_dev
+ * (src/inference/decoder.c:950-958). delta may be NULL (plain norm). */
+int orc_add_rmsnorm_f16(uint16_t* hidden, const uint16_t* delta,
+                        const uint16_t* w_f16, uint16_t* normed,
+                        int rows, int n, float eps) {
+    if (!hidden || !w_f16 || !normed) return ORC_ERR_NULL_PTR;
+    const size_t total = (size_t)rows * (size_t)n;
+    float* h = (float*)malloc(sizeof(float) * (total ? total : 1));
+    float* y = (float*)malloc(sizeof(float) * (total ? total : 1));
+    if (!h || !y) { free(h); free(y); return ORC_ERR_INVALID_ARG; }
+    orc_widen_f16(hidden, h, total);
+    if (delta) {
+        float* d = (float*)malloc(sizeof(float) * (total ? total : 1));
+        if (!d) { free(h); free(y); return ORC_ERR_INVALID_ARG; }
+        orc_widen_f16(delta, d, total);
+        orc_residual_add(h, d, total);
+        free(d);
+        orc_round_f16(h, hidden, total);
+        orc_widen_f16(hidden, h, total);
+    }
+    int st = orc_rmsnorm(h, w_f16, y, rows, n, eps);
+    if (st == ORC_OK) orc_round_f16(y, normed, total);
+    free(h); free(y);
+    return st;
+}
+
+int orc_rope_f16(uint16_t* x, int rows, int n_heads, int head_dim,
+                 int position_offset, float theta) {
+    if (!x) return ORC_ERR_NULL_PTR;
+    const size_t total = (size_t)rows * (size_t)n_heads * (size_t)head_dim;
+    float* f = (float*)malloc(sizeof(float) * (total ? total : 1));
+    if (!f) return ORC_ERR_INVALID_ARG;
+    orc_widen_f16(x, f, total);
+    int st = orc_rope(f, rows, n_heads, head_dim, position_offset, theta);
+    if (st == ORC_OK) orc_round_f16(f, x, total);
+    free(f);
+    return st;
+}
+
+int orc_swiglu_f16(const uint16_t* gate, const uint16_t* up, uint16_t* out, size_t n) {
+    if (!gate || !up || !out) return ORC_ERR_NULL_PTR;
+    ptrdiff_t i;
+#pragma omp parallel for schedule(static)
+    for (i = 0; i < (ptrdiff_t)n; i++) {
+        const float g = orc_half_to_float(gate[i]);
+        const float u = orc_half_to_float(up[i]);
+        const float den = 1.0f + expf(-g);
+        const float act = g / den;
+        out[i] = orc_float_to_half_rne(act * u);
+    }
+    return ORC_OK;
+}
+
+int orc_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
