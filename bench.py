@@ -1,0 +1,419 @@
+#!/usr/bin/env python
+"""bench.py -- the layer chain (residual add + RMSNorm, RoPE on Q/K, SwiGLU) at
+long-prompt prefill: T = 14449 tokens of the Qwen2-7B shape, token-sharded over
+the GPUs of one box with no collective on the data path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W]        # this library
+  python bench.py --impl reference [...]                     # the reference's CPU kernels
+
+A step is one pass of the three kernels over the rank's rows. `value` is
+aggregate tokens/s with inputs resident in HBM (CUDA events, max over ranks);
+`e2e` is the same metric through the host-buffer API with the host->device and
+device->host copies of every step inside the timed region. `roofline` is for
+the kernel that moves most of the bytes (SwiGLU); `kernels` lists all three.
+For N > 1 launch under torch.distributed.run (one rank per GPU); a bare
+`--gpus N` re-launches itself that way.
+
+Synthetic data: seeded N(0,1) FP16 activations, gamma ~ N(1, 0.02), in the
+model's shapes; there are no weights on this path.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "vibevoice.c_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+# Qwen2-7B decoder shape and the prompt length of the reference's long-file run
+T_TOTAL, H, NQ, NKV, HD, INTER = 14449, 3584, 28, 4, 128, 18944
+EPS, THETA, SEED = 1e-6, 1e6, 1
+# algorithmic bytes per token: every tensor read once and written once, FP16
+BYTES_ADDNORM = 4 * H * 2                 # read h, delta; write h', normed      28 672
+BYTES_ROPE = 2 * (NQ + NKV) * HD * 2      # read + write Q and K                 16 384
+BYTES_SWIGLU = 3 * INTER * 2              # read gate, up; write out            113 664
+BYTES_CHAIN = BYTES_ADDNORM + BYTES_ROPE + BYTES_SWIGLU   #                     158 720
+FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes per token per launch seen by ncu (dram__bytes_read.sum +
+# dram__bytes_write.sum), from the captures summarised under profiles/;
+# None until a capture exists.
+NCU_DRAM_BYTES_PER_TOKEN = {"swiglu": None, "add_rmsnorm": None, "rope_qk": None}
+CPU_SAMPLE_ROWS = 4096
+
+
+def measured_hbm_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Polls SM clock and throttle reasons of one GPU through NVML (read-only)
+    while the benchmark runs."""
+
+    def __init__(self, uuid: str | None, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid) if uuid else pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append((time.perf_counter(), nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self, t0=None, t1=None):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=1.0)
+        inside = [m for (t, m) in self.samples if t0 is None or (t0 <= t <= t1)]
+        use = inside if len(inside) >= 3 else [m for _, m in self.samples]
+        return {
+            "sm_mhz": statistics.median(use) if use else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(use),
+            "window": "timed region" if len(inside) >= 3 else "warm-up + timed passes",
+        }
+
+
+# --------------------------------------------------------------------------- CPU legs
+def cpu_chain_run(rows: int, steps: int, warmup: int):
+    """The reference's CPU path for one layer's elementwise chain on FP32
+    activations (src/inference/decoder.c:1463-1473): residual add, RMSNorm,
+    RoPE on Q and K, SwiGLU in place. Uses the compiled reference kernels when
+    present, else the restatement. Returns (tokens/s, info)."""
+    import ctypes as C
+    import numpy as np
+    import oracle
+    rng = np.random.default_rng(SEED)
+    f = lambda *s: rng.standard_normal(s, dtype=np.float32)
+    h, d, q, k, gate, up = f(rows, H), f(rows, H), f(rows, NQ, HD), f(rows, NKV, HD), f(rows, INTER), f(rows, INTER)
+    w = (1 + 0.02 * rng.standard_normal(H)).astype(np.float16)
+    normed = np.empty_like(h)
+    fp = lambda a: a.ctypes.data_as(C.POINTER(C.c_float))
+    if oracle.have_reference():
+        ref = oracle.reference()
+        L, kind = ref.lib, "reference"
+        threads = ref.threads()          # physical cores, pinned (cpu_kernels.c:303-327)
+        simd, cores = ref.simd_name(), ref.physical_cores()
+
+        def step():
+            L.vv_residual_add_cpu(fp(h), fp(d), h.size)
+            L.vv_rmsnorm_cpu(fp(h), w.ctypes.data, fp(normed), rows, H, C.c_float(EPS))
+            L.vv_rope_cpu(fp(q), rows, NQ, HD, 0, C.c_float(THETA))
+            L.vv_rope_cpu(fp(k), rows, NKV, HD, 0, C.c_float(THETA))
+            L.vv_swiglu_cpu(fp(gate), fp(up), fp(gate), gate.size)
+    else:
+        R = oracle.restated()
+        L, kind = R.lib, "port"
+        threads, simd, cores = R.threads(), "scalar", os.cpu_count()
+        u16 = C.POINTER(C.c_uint16)
+
+        def step():
+            L.orc_residual_add(fp(h), fp(d), h.size)
+            L.orc_rmsnorm(fp(h), w.view(np.uint16).ctypes.data_as(u16), fp(normed), rows, H, C.c_float(EPS))
+            L.orc_rope(fp(q), rows, NQ, HD, 0, C.c_float(THETA))
+            L.orc_rope(fp(k), rows, NKV, HD, 0, C.c_float(THETA))
+            L.orc_swiglu(fp(gate), fp(up), fp(gate), gate.size)
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = time.perf_counter() - t0
+    info = {"kind": kind, "cores": threads, "physical_cores": cores, "simd": simd,
+            "sample": f"{rows} of {T_TOTAL} rows per pass, {steps} passes after {warmup} warm-up, FP32 activations "
+                      f"(the CPU path's type; 2x the FP16 bytes)", "ms_per_pass": 1e3 * dt / steps}
+    return rows * steps / dt, info
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = T_TOTAL
+    value, info = cpu_chain_run(rows, args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": "layer_chain_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": info["ms_per_pass"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": info["cores"], "kind": info["kind"],
+                         "sample": info["sample"], "simd": info["simd"], "physical_cores": info["physical_cores"]},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus, scaling="strong"):
+    return {
+        "workload": "Qwen2-7B layer chain at long-prompt prefill: add+RMSNorm [T,3584], RoPE Q [T,28,128] K [T,4,128] "
+                    "at positions 0..T-1, SwiGLU [T,18944] in place; T=14449, fp16 ~ N(0,1), seed 1",
+        "rows_total": T_TOTAL * (n_gpus if scaling == "weak" else 1),
+        "sharding": f"contiguous token rows over {n_gpus} GPU(s), no collective",
+        "eps": EPS, "theta": THETA,
+        "l2": "inputs larger than L2: every rank's working set exceeds the 126 MB L2 and each pass streams it once",
+    }
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_native(args):
+    import torch
+    import torch.distributed as dist
+    import vvb200 as vv
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE {world}"
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def reduce_max(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def reduce_sum(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    total_rows = T_TOTAL * (world if args.scaling == "weak" else 1)
+    first, rows = vv.vvb_shard_rows(total_rows, world, rank)
+
+    # The same seeded tensors on every rank count; each rank draws its own rows
+    # (seed, first row) -- values do not affect timing, parity is tested elsewhere.
+    gen = torch.Generator(device=dev).manual_seed(SEED + 1000 * rank)
+    mk = lambda *s: torch.randn(*s, generator=gen, device=dev).half()
+    h, d = mk(rows, H), mk(rows, H)
+    w = (1 + 0.02 * torch.randn(H, generator=gen, device=dev)).half()
+    q, k = mk(rows, NQ, HD), mk(rows, NKV, HD)
+    gate, up = mk(rows, INTER), mk(rows, INTER)
+    normed = torch.empty_like(h)
+    h0, g0 = h.clone(), gate.clone()
+    chain = vv.make_chain(h, d, w, normed, q, k, gate, up, rows, H, NQ, NKV, HD, INTER, first, EPS, THETA)
+    stream = torch.cuda.current_stream()
+
+    def restore():
+        # the chain works in place; start every pass set from the same values
+        h.copy_(h0)
+        gate.copy_(g0)
+
+    def step():
+        vv.check(vv.vvb_layer_chain_dev(chain, stream), "vvb_layer_chain_dev")
+
+    sampler = None
+    if rank == 0:
+        uuid = None
+        try:
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(local).uuid)
+        except Exception:
+            pass
+        sampler = ClockSampler(uuid, local)
+        sampler.start()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+
+    # ---- pass A: K steps back to back, one event pair; this is `value`
+    restore()
+    torch.cuda.synchronize()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = vv.launch_count()
+    t_region0 = time.perf_counter()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    t_region1 = time.perf_counter()
+    launches = vv.launch_count() - launches0
+    barrier()
+    ms_total = reduce_max(e0.elapsed_time(e1))
+    launches_all = int(reduce_sum(float(launches)))
+
+    # ---- pass B: the same K steps with an event between launches: per-kernel durations
+    restore()
+    torch.cuda.synchronize()
+    barrier()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    for s in range(args.steps):
+        ev[s][0].record(stream)
+        vv.check(vv.vvb_add_rmsnorm_dev(h, d, w, normed, rows, H, EPS, stream))
+        ev[s][1].record(stream)
+        vv.check(vv.vvb_rope_qk_dev(q, k, rows, NQ, NKV, HD, first, None, THETA, stream))
+        ev[s][2].record(stream)
+        vv.check(vv.vvb_swiglu_dev(gate, up, gate, rows * INTER, stream))
+        ev[s][3].record(stream)
+    torch.cuda.synchronize()
+    barrier()
+    per = {}
+    for i, name in enumerate(("add_rmsnorm", "rope_qk", "swiglu")):
+        per[name] = reduce_max(statistics.fmean(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)))
+    ms_total_b = reduce_max(ev[0][0].elapsed_time(ev[-1][3]))
+
+    clocks = sampler.stop(t_region0, t_region1) if sampler else None
+
+    # ---- e2e: host buffers through the pipeline API, copies inside the timed region
+    pin = lambda t: t.cpu().pin_memory()
+    hh, hd_, hw, hq, hk, hg, hu = (pin(t) for t in (h0, d, w, q, k, g0, up))
+    hn = torch.empty_like(hh).pin_memory()
+    pipe = vv.HostPipeline(local, args.slice_rows, H, NQ, NKV, HD, INTER)
+    hchain = vv.make_chain(hh, hd_, hw, hn, hq, hk, hg, hu, rows, H, NQ, NKV, HD, INTER, first, EPS, THETA)
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    for _ in range(2):
+        vv.check(pipe.run(hchain), "vvb_layer_chain_host")
+    barrier()
+    dev_ms, t0 = 0.0, time.perf_counter()
+    for _ in range(e2e_steps):
+        vv.check(pipe.run(hchain), "vvb_layer_chain_host")
+        dev_ms += pipe.last_ms()
+    wall_ms = 1e3 * (time.perf_counter() - t0)
+    h2d, d2h = pipe.last_traffic()
+    barrier()
+    e2e_ms = reduce_max(dev_ms)
+    e2e_wall_ms = reduce_max(wall_ms)
+    h2d_all, d2h_all = int(reduce_sum(float(h2d))), int(reduce_sum(float(d2h)))
+    pipe.close()
+
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+
+    peak, peak_kind = measured_hbm_peak()
+    rows_max = -(-total_rows // world)       # the slowest rank holds ceil(T/N) rows
+    kernels = {}
+    for name, bpt in (("add_rmsnorm", BYTES_ADDNORM), ("rope_qk", BYTES_ROPE), ("swiglu", BYTES_SWIGLU)):
+        gbs = bpt * rows_max / (per[name] * 1e-3) / 1e9
+        kernels[name] = {"ms": per[name], "GB/s": gbs, "frac_of_" + peak_kind: gbs / peak,
+                         "algorithmic_bytes_per_launch": bpt * rows_max}
+    top = "swiglu"
+    traffic = NCU_DRAM_BYTES_PER_TOKEN[top]
+    line = {
+        "metric": "layer_chain_tokens_per_s", "value": total_rows * args.steps / (ms_total * 1e-3),
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": args.scaling,
+        "vs_baseline": None, "dtype": "f16 storage, f32 arithmetic (f64 sum of squares)", "data": "synthetic",
+        "config": workload_config(world, args.scaling),
+        "chain_GB/s_per_gpu": BYTES_CHAIN * rows_max / (ms_total / args.steps * 1e-3) / 1e9,
+        "roofline": {"bound": "hbm", "kernel": top, "achieved": kernels[top]["GB/s"], "peak": peak, "unit": "GB/s",
+                     "frac": kernels[top]["GB/s"] / peak, "peak_kind": "of " + peak_kind,
+                     "traffic": None if traffic is None else traffic * rows_max,
+                     "timing": "CUDA events around every launch on the launching stream, mean over the K steps of "
+                               "a second pass of the same workload; ms_per_step_with_events = "
+                               f"{ms_total_b / args.steps:.4f}"},
+        "kernels": kernels,
+        "e2e": {"value": total_rows * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": h2d_all, "d2h_bytes_per_step": d2h_all, "steps": e2e_steps,
+                "ms_per_step": e2e_ms / e2e_steps, "wall_ms_per_step": e2e_wall_ms / e2e_steps,
+                "api": "vvb_layer_chain_host (pinned host tensors; uploads, kernels and downloads pipelined in "
+                       f"{args.slice_rows}-row slices)"},
+        "gpu_launches": launches_all,
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_subprocess()
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline_subprocess():
+    """Times the CPU leg in a child process: the reference pins its OpenMP team
+    (and the calling thread) to cores, which must not leak into this process."""
+    try:
+        out = subprocess.run([sys.executable, os.path.abspath(__file__), "--cpu-baseline-worker"],
+                             capture_output=True, text=True, timeout=600, check=True).stdout
+        return json.loads(out.strip().splitlines()[-1])
+    except Exception as e:  # the GPU line is still valid without it
+        return {"value": None, "unit": "tokens/s", "error": f"{type(e).__name__}: {e}"[:200]}
+
+
+def cpu_baseline_worker():
+    value, info = cpu_chain_run(CPU_SAMPLE_ROWS, steps=20, warmup=2)
+    print(json.dumps({"value": value, "unit": "tokens/s", "cores": info["cores"], "kind": info["kind"],
+                      "sample": info["sample"], "simd": info["simd"], "physical_cores": info["physical_cores"]}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["native", "reference"], default="native")
+    ap.add_argument("--scaling", choices=["strong", "weak"], default="strong",
+                    help="strong: T=14449 rows in total (the named config); weak: 14449 rows per GPU")
+    ap.add_argument("--slice-rows", type=int, default=1024, help="rows per slice of the host-buffer pipeline")
+    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-baseline-worker", action="store_true", help=argparse.SUPPRESS)
+    args = ap.parse_args()
+
+    if args.cpu_baseline_worker:
+        return cpu_baseline_worker()
+    if args.gpus > 1 and "RANK" not in os.environ:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 1000),
+               os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_native(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,219 @@
+/**
+ * @file vvb200.h
+ * @brief C-ABI of libvvb200: the Qwen2-7B decoder's per-token layer kernels
+ *        (residual add + RMSNorm, RoPE on Q/K, SwiGLU, embedding gather),
+ *        hand-written CUDA for sm_100a behind vibevoice.c's device op names.
+ *
+ * The first group of functions has exactly the names, argument lists and
+ * argument meaning of the reference's accelerator op set for this path, so a
+ * build of the reference that leaves out its own rmsnorm.cu / rope.cu /
+ * swiglu.cu / embedding.cu / conv_vae.cu and links this library resolves the
+ * same symbols (the reference picks its backend at link time:
+ * include/vibevoice/device.h:11-14). The second group (vvb_*) is additive:
+ * fused forms that save HBM passes, a host-buffer pipeline, and the row
+ * partition used to shard tokens over the GPUs of one box.
+ *
+ * Conventions (those of include/vibevoice/device.h:16-21):
+ *   - every tensor pointer is caller-owned DEVICE memory of the current
+ *     device, FP16 (IEEE binary16) unless the name says otherwise, row-major,
+ *     contiguous; ids are int32 in device memory;
+ *   - `void* stream` is a cudaStream_t; NULL is the legacy default stream;
+ *   - work is enqueued and the call returns; nothing synchronises, allocates,
+ *     frees or keeps a pointer, so every *_dev call may be stream-captured;
+ *   - calls are re-entrant: no file-scope mutable state;
+ *   - the return value is a vv_status_t code; nothing throws, aborts or logs;
+ *   - rows == 0 / n == 0 is VV_OK and launches nothing;
+ *   - there is no CPU fallback anywhere: without a usable CUDA device the
+ *     calls return VV_ERR_CUDA / VV_ERR_CUDA_LAUNCH.
+ *
+ * Pointers that are 16-byte aligned with row widths that are multiples of 8
+ * halves take the 128-bit paths; anything else takes slower scalar kernels
+ * with the same results.
+ */
+#ifndef VVB200_H
+#define VVB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes: numerically those of include/vibevoice/types.h:18-58. When
+ * the reference's own types.h is in scope its enum is used instead. */
+#ifndef VV_TYPES_H
+typedef enum vv_status {
+    VV_OK = 0,
+    VV_ERR_INVALID_ARG = -1,
+    VV_ERR_NULL_PTR = -2,
+    VV_ERR_OUT_OF_MEMORY = -3,
+    VV_ERR_UNSUPPORTED = -7,
+    VV_ERR_OVERFLOW = -8,
+    VV_ERR_CUDA = -100,
+    VV_ERR_CUDA_OOM = -101,
+    VV_ERR_CUDA_LAUNCH = -102
+} vv_status_t;
+#endif
+
+/* ====================================================================== *
+ *  Group 1 -- the reference's op names (drop-in)                          *
+ * ====================================================================== */
+
+/** out[p, :] = table[ids[p], :], a bit copy. Replaces
+ *  include/vibevoice/device.h:486-488 (src/cuda/embedding.cu:59). Like the
+ *  reference it cannot range-check ids (the table height is not an argument);
+ *  vvb_embedding_rmsnorm_dev takes the height and clamps. */
+vv_status_t vv_embedding_dev(const void* table, const int32_t* ids, void* output,
+                             int seq_len, int hidden_size, void* stream);
+
+/** Per row: y = f16((x * inv) * w), inv = 1/sqrt(mean(x^2) + eps); the sum of
+ *  squares is accumulated in double, as the reference's CPU kernel does.
+ *  input == output is allowed. Correct for any hidden_size >= 1. Replaces
+ *  include/vibevoice/device.h:490-492 (src/cuda/rmsnorm.cu:82). */
+vv_status_t vv_rmsnorm_dev(const void* input, const void* weight, void* output,
+                           int seq_len, int hidden_size, float eps, void* stream);
+
+/** RoPE in place over x[seq_len, n_heads, head_dim], pairs (i, i + head_dim/2),
+ *  freq_i = powf(theta, -2i/head_dim) taken from the HOST libm, angle =
+ *  (float)pos * freq_i, pos = row + (d_position ? *d_position : position_offset).
+ *  head_dim must be even and <= 512 (VV_ERR_UNSUPPORTED beyond). Replaces
+ *  include/vibevoice/device.h:494-502 (src/cuda/rope.cu:89). */
+vv_status_t vv_rope_dev(void* x, int seq_len, int n_heads, int head_dim,
+                        int position_offset, const int* d_position, float theta,
+                        void* stream);
+
+/** out[i] = f16( (g / (1 + exp(-g))) * up[i] ), g = gate[i]; output == gate
+ *  (the engine's call, src/inference/decoder.c:977) and output == up are
+ *  allowed. Replaces include/vibevoice/device.h:504-506 (src/cuda/swiglu.cu:79). */
+vv_status_t vv_swiglu_dev(const void* gate, const void* up, void* output,
+                          int n_elements, void* stream);
+
+/** SwiGLU where row r of gate_up[rows, 2*inter] holds gate then up; output is
+ *  [rows, inter]. Replaces include/vibevoice/device.h:508-510, which the
+ *  reference declares and implements only for Metal
+ *  (src/metal/kernels/transformer.metal:94-106). */
+vv_status_t vv_swiglu_fused_dev(const void* gate_up, void* output, int rows,
+                                int inter, void* stream);
+
+/** x[i] = f16(float(x[i]) + float(y[i])). Replaces
+ *  include/vibevoice/device.h:512 (src/cuda/conv_vae.cu:37). */
+vv_status_t vv_residual_add_dev(void* x, const void* y, int total, void* stream);
+
+/** output[m, j] = f16(float(output[m, j]) + float(bias[j])). Replaces
+ *  include/vibevoice/device.h:513-514 (src/cuda/conv_vae.cu:72). */
+vv_status_t vv_bias_add_dev(void* output, const void* bias, int M, int N, void* stream);
+
+/** FP32 <-> FP16 (round to nearest even). Replace
+ *  include/vibevoice/device.h:717-720 (src/cuda/conv_vae.cu:100-116), which
+ *  live in the same translation unit as the residual add. */
+vv_status_t vv_fp32_to_fp16_dev(const void* in_fp32, void* out_fp16, int n, void* stream);
+vv_status_t vv_fp16_to_fp32_dev(const void* in_fp16, void* out_fp32, int n, void* stream);
+
+/* ====================================================================== *
+ *  Group 2 -- additive entry points (no counterpart symbol in the          *
+ *  reference; each states the reference call sequence it equals)           *
+ * ====================================================================== */
+
+/** hidden = f16(hidden + delta); normed = rmsnorm(hidden) -- one kernel, four
+ *  HBM passes instead of the five of vv_residual_add_dev followed by
+ *  vv_rmsnorm_dev (src/inference/decoder.c:950-958 and :988 with the next
+ *  layer's :810). delta == normed_out is allowed (the engine reuses that
+ *  buffer); delta == NULL skips the add and leaves hidden untouched. */
+vv_status_t vvb_add_rmsnorm_dev(void* hidden_inout, const void* delta,
+                                const void* weight, void* normed_out,
+                                int rows, int hidden_size, float eps, void* stream);
+
+/** vv_rope_dev on Q[rows, n_q_heads, head_dim] and K[rows, n_kv_heads,
+ *  head_dim] in one launch, cos/sin computed once per row for both
+ *  (src/inference/decoder.c:850-855 issues two launches). Either of q, k may
+ *  be NULL with a head count of 0. */
+vv_status_t vvb_rope_qk_dev(void* q, void* k, int rows, int n_q_heads, int n_kv_heads,
+                            int head_dim, int position_offset, const int* d_position,
+                            float theta, void* stream);
+
+/** hidden_out[p] = table[clamp(ids[p], 0, vocab-1)] (bit copy) and
+ *  normed_out[p] = rmsnorm(hidden_out[p]) in one kernel: the gather of
+ *  src/inference/pipeline.c:2309 fused with layer 0's first norm
+ *  (decoder.c:810). vocab <= 0 disables the clamp. normed_out may be NULL
+ *  (gather only, weight ignored). */
+vv_status_t vvb_embedding_rmsnorm_dev(const void* table, const int32_t* ids,
+                                      void* hidden_out, const void* weight,
+                                      void* normed_out, int rows, int hidden_size,
+                                      int vocab, float eps, void* stream);
+
+/** Sizes above INT_MAX elements for the flat ops (the reference's `int`
+ *  counts stop at 2^31-1, about 113k rows of 18944). */
+vv_status_t vvb_swiglu_dev(const void* gate, const void* up, void* output,
+                           size_t n_elements, void* stream);
+vv_status_t vvb_residual_add_dev(void* x, const void* y, size_t total, void* stream);
+
+/** One decoder layer's elementwise chain on one stream, in the engine's
+ *  order: add + RMSNorm, RoPE on Q and K, SwiGLU in place on gate
+ *  (src/inference/decoder.c:950-977). Three launches. */
+typedef struct vvb_layer_chain {
+    void* hidden;          /* [rows, hidden_size] in/out */
+    const void* delta;     /* [rows, hidden_size] */
+    const void* norm_w;    /* [hidden_size] */
+    void* normed;          /* [rows, hidden_size] out */
+    void* q;               /* [rows, n_q_heads, head_dim] in place */
+    void* k;               /* [rows, n_kv_heads, head_dim] in place */
+    void* gate;            /* [rows, inter] in/out (receives silu(gate)*up) */
+    const void* up;        /* [rows, inter] */
+    int rows, hidden_size, n_q_heads, n_kv_heads, head_dim, inter;
+    int position_offset;   /* position of row 0 (a shard passes its first row) */
+    float eps, theta;
+} vvb_layer_chain_t;
+vv_status_t vvb_layer_chain_dev(const vvb_layer_chain_t* c, void* stream);
+
+/* ---- token-row sharding over the GPUs of one box (no collective) -------- */
+
+/** Rows [*first, *first + *count) of `total_rows` that part `part` of `parts`
+ *  owns: contiguous blocks of ceil(total/parts), the last ones shorter or
+ *  empty. RoPE on a shard passes *first as position_offset. */
+vv_status_t vvb_shard_rows(int64_t total_rows, int parts, int part,
+                           int64_t* first, int64_t* count);
+
+/* ---- host-buffer pipeline ------------------------------------------------ */
+
+/** A per-device context that owns staging buffers, streams and events, for
+ *  callers whose tensors live in HOST memory. Not a CPU fallback: the math
+ *  runs on the GPU; this only moves rows host -> device -> host in slices so
+ *  that copies in both directions overlap the kernels. */
+typedef struct vvb_host_ctx vvb_host_ctx_t;
+
+/** Creates a context on `device` able to process slices of up to
+ *  `max_slice_rows` rows of the given layer shape. */
+vv_status_t vvb_host_ctx_create(vvb_host_ctx_t** out, int device, int max_slice_rows,
+                                int hidden_size, int n_q_heads, int n_kv_heads,
+                                int head_dim, int inter);
+void vvb_host_ctx_destroy(vvb_host_ctx_t* ctx);
+
+/** vvb_layer_chain_dev with every tensor pointer in HOST memory (pinned for
+ *  full speed; pageable works but serialises). Blocks until the results are
+ *  back in host memory. */
+vv_status_t vvb_layer_chain_host(vvb_host_ctx_t* ctx, const vvb_layer_chain_t* host_tensors);
+
+/** Bytes moved host->device and device->host by the last
+ *  vvb_layer_chain_host call on this context. */
+void vvb_host_ctx_last_traffic(const vvb_host_ctx_t* ctx, uint64_t* h2d_bytes, uint64_t* d2h_bytes);
+
+/** Device-side duration of the last vvb_layer_chain_host call on this context
+ *  in milliseconds, from CUDA events recorded before its first upload and
+ *  after its last download. */
+float vvb_host_ctx_last_ms(const vvb_host_ctx_t* ctx);
+
+/* ---- introspection ------------------------------------------------------ */
+
+/** "vvb200 <version> sm_100a". */
+const char* vvb_version(void);
+/** Short text for a status code. */
+const char* vvb_status_string(int status);
+/** Number of kernel launches this library has enqueued in this process
+ *  (a relaxed atomic counter; for benchmarks that must state launch counts). */
+uint64_t vvb_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VVB200_H */

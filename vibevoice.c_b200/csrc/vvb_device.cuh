@@ -1,0 +1,63 @@
+/*
+ * vvb_device.cuh -- device-side helpers shared by the sm_100a kernels:
+ * 128-bit streaming loads/stores, FP16 pack/unpack, warp reductions.
+ *
+ * Everything on this path is read once and written once, so loads and stores
+ * carry the streaming (evict-first) cache operator; the only reused data
+ * (gamma, cos/sin) is staged in shared memory by the kernels themselves.
+ */
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace vvb {
+
+/* One 16-byte vector = 8 halves. */
+typedef uint4 vec16;
+
+__device__ __forceinline__ vec16 ld_stream(const vec16* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(vec16* p, const vec16& v) { __stcs(p, v); }
+
+__device__ __forceinline__ float2 unpack2(uint32_t u) {
+    __half2 h = *reinterpret_cast<const __half2*>(&u);
+    return __half22float2(h);
+}
+/* Two floats -> two halves, each rounded to nearest even (what __float2half
+ * does); low half = a. */
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__device__ __forceinline__ void unpack8(const vec16& v, float (&f)[8]) {
+    float2 t;
+    t = unpack2(v.x); f[0] = t.x; f[1] = t.y;
+    t = unpack2(v.y); f[2] = t.x; f[3] = t.y;
+    t = unpack2(v.z); f[4] = t.x; f[5] = t.y;
+    t = unpack2(v.w); f[6] = t.x; f[7] = t.y;
+}
+__device__ __forceinline__ vec16 pack8(const float (&f)[8]) {
+    vec16 v;
+    v.x = pack2(f[0], f[1]);
+    v.y = pack2(f[2], f[3]);
+    v.z = pack2(f[4], f[5]);
+    v.w = pack2(f[6], f[7]);
+    return v;
+}
+
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+/* 16-byte asynchronous copy global -> shared (LDGSTS), L2-only caching. */
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
+}  // namespace vvb

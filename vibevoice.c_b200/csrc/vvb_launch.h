@@ -1,0 +1,53 @@
+/*
+ * vvb_launch.h -- the thin C-ABI between the C11 host layer (the host/ directory) and
+ * the CUDA translation units (the csrc/ directory). Each function enqueues exactly the
+ * kernels named on `stream` of the current device and returns the
+ * cudaError_t of the launch as an int (0 = cudaSuccess). Arguments were
+ * validated by the caller; these do no checking beyond choosing a kernel
+ * variant from sizes and alignment.
+ */
+#ifndef VVB_LAUNCH_H
+#define VVB_LAUNCH_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VVB_ROPE_MAX_HALF 256 /* head_dim/2 entries carried in kernel parameters */
+
+/* Row kernels (csrc/row_norm.cu).
+ *   src_rows : [rows, hidden] FP16 (or the table when ids != NULL)
+ *   delta    : NULL or [rows, hidden]
+ *   ids      : NULL or int32[rows] (gather source rows from src_rows)
+ *   row_out  : NULL or [rows, hidden]: receives the gathered / summed row
+ *   weight   : [hidden] (ignored when normed == NULL)
+ *   normed   : NULL or [rows, hidden] */
+int vvbk_row_norm(const void* src_rows, const void* delta, const int32_t* ids, int vocab,
+                  void* row_out, const void* weight, void* normed,
+                  int rows, int hidden, float eps, void* stream);
+
+/* RoPE (csrc/rope.cu). inv_freq holds head_dim/2 host-computed floats. */
+int vvbk_rope(void* q, void* k, int rows, int n_q_heads, int n_kv_heads, int head_dim,
+              int position_offset, const int* d_position, const float* inv_freq, void* stream);
+
+/* SwiGLU (csrc/swiglu.cu). Flat: gate/up/out of n elements. Fused: rows of
+ * [gate | up] with 2*inter halves per row. */
+int vvbk_swiglu(const void* gate, const void* up, void* out, size_t n, void* stream);
+int vvbk_swiglu_fused(const void* gate_up, void* out, int rows, int inter, void* stream);
+
+/* Flat elementwise ops (csrc/elementwise.cu). */
+int vvbk_residual_add(void* x, const void* y, size_t n, void* stream);
+int vvbk_bias_add(void* out, const void* bias, int M, int N, void* stream);
+int vvbk_f32_to_f16(const void* in, void* out, size_t n, void* stream);
+int vvbk_f16_to_f32(const void* in, void* out, size_t n, void* stream);
+
+/* Launches enqueued so far in this process. */
+uint64_t vvbk_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

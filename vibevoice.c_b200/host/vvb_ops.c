@@ -1,0 +1,187 @@
+/*
+ * vvb_ops.c -- C11 host layer of libvvb200: the exported entry points.
+ *
+ * Each entry validates its arguments the way the reference's launchers do
+ * (NULL tensors -> VV_ERR_NULL_PTR: src/cuda/rmsnorm.cu:86, rope.cu:93,
+ * swiglu.cu:83, embedding.cu:63; a failed launch -> VV_ERR_CUDA_LAUNCH), adds
+ * the checks the reference leaves to luck (negative sizes, products that
+ * overflow), and hands the work to the CUDA translation units through the
+ * launch interface in csrc/vvb_launch.h. No CUDA call is made here except
+ * through that interface; there is no CPU implementation of any op in this
+ * library.
+ */
+#include "vvb200.h"
+#include "../csrc/vvb_launch.h"
+
+#include <limits.h>
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#define VVB_VERSION "0.1.0"
+
+static vv_status_t from_cuda(int err) { return err == 0 ? VV_OK : VV_ERR_CUDA_LAUNCH; }
+
+/* ------------------------------------------------------------------ group 1 */
+
+vv_status_t vv_embedding_dev(const void* table, const int32_t* ids, void* output,
+                             int seq_len, int hidden_size, void* stream) {
+    if (!table || !ids || !output) return VV_ERR_NULL_PTR;
+    if (seq_len < 0 || hidden_size < 0) return VV_ERR_INVALID_ARG;
+    if (seq_len == 0 || hidden_size == 0) return VV_OK;
+    return from_cuda(vvbk_row_norm(table, NULL, ids, 0, output, NULL, NULL,
+                                   seq_len, hidden_size, 0.0f, stream));
+}
+
+vv_status_t vv_rmsnorm_dev(const void* input, const void* weight, void* output,
+                           int seq_len, int hidden_size, float eps, void* stream) {
+    if (!input || !weight || !output) return VV_ERR_NULL_PTR;
+    if (seq_len < 0 || hidden_size < 0) return VV_ERR_INVALID_ARG;
+    if (seq_len == 0 || hidden_size == 0) return VV_OK;
+    return from_cuda(vvbk_row_norm(input, NULL, NULL, 0, NULL, weight, output,
+                                   seq_len, hidden_size, eps, stream));
+}
+
+/* freq_i = powf(theta, -2i/head_dim): the very expression of the reference's
+ * CPU kernel (src/cpu/cpu_kernels.c:1468), evaluated by the host libm so the
+ * device sees the same 32-bit values the CPU path uses. */
+static void fill_inv_freq(float* out, int head_dim, float theta) {
+    for (int i = 0; i < head_dim / 2; i++)
+        out[i] = powf(theta, -2.0f * (float)i / (float)head_dim);
+}
+
+vv_status_t vvb_rope_qk_dev(void* q, void* k, int rows, int n_q_heads, int n_kv_heads,
+                            int head_dim, int position_offset, const int* d_position,
+                            float theta, void* stream) {
+    if (rows < 0 || n_q_heads < 0 || n_kv_heads < 0 || head_dim < 0) return VV_ERR_INVALID_ARG;
+    if ((n_q_heads > 0 && !q) || (n_kv_heads > 0 && !k)) return VV_ERR_NULL_PTR;
+    if (rows == 0 || n_q_heads + n_kv_heads == 0 || head_dim < 2) return VV_OK;
+    if (head_dim / 2 > VVB_ROPE_MAX_HALF) return VV_ERR_UNSUPPORTED;
+    float inv_freq[VVB_ROPE_MAX_HALF];
+    fill_inv_freq(inv_freq, head_dim, theta);
+    return from_cuda(vvbk_rope(q, k, rows, n_q_heads, n_kv_heads, head_dim,
+                               position_offset, d_position, inv_freq, stream));
+}
+
+vv_status_t vv_rope_dev(void* x, int seq_len, int n_heads, int head_dim,
+                        int position_offset, const int* d_position, float theta,
+                        void* stream) {
+    if (!x) return VV_ERR_NULL_PTR;
+    return vvb_rope_qk_dev(x, NULL, seq_len, n_heads, 0, head_dim, position_offset,
+                           d_position, theta, stream);
+}
+
+vv_status_t vvb_swiglu_dev(const void* gate, const void* up, void* output,
+                           size_t n_elements, void* stream) {
+    if (!gate || !up || !output) return VV_ERR_NULL_PTR;
+    if (n_elements == 0) return VV_OK;
+    return from_cuda(vvbk_swiglu(gate, up, output, n_elements, stream));
+}
+
+vv_status_t vv_swiglu_dev(const void* gate, const void* up, void* output,
+                          int n_elements, void* stream) {
+    if (!gate || !up || !output) return VV_ERR_NULL_PTR;
+    if (n_elements < 0) return VV_ERR_INVALID_ARG;
+    return vvb_swiglu_dev(gate, up, output, (size_t)n_elements, stream);
+}
+
+vv_status_t vv_swiglu_fused_dev(const void* gate_up, void* output, int rows,
+                                int inter, void* stream) {
+    if (!gate_up || !output) return VV_ERR_NULL_PTR;
+    if (rows < 0 || inter < 0) return VV_ERR_INVALID_ARG;
+    if (rows == 0 || inter == 0) return VV_OK;
+    return from_cuda(vvbk_swiglu_fused(gate_up, output, rows, inter, stream));
+}
+
+vv_status_t vvb_residual_add_dev(void* x, const void* y, size_t total, void* stream) {
+    if (!x || !y) return VV_ERR_NULL_PTR;
+    if (total == 0) return VV_OK;
+    return from_cuda(vvbk_residual_add(x, y, total, stream));
+}
+
+vv_status_t vv_residual_add_dev(void* x, const void* y, int total, void* stream) {
+    if (!x || !y) return VV_ERR_NULL_PTR;
+    if (total < 0) return VV_ERR_INVALID_ARG;
+    return vvb_residual_add_dev(x, y, (size_t)total, stream);
+}
+
+vv_status_t vv_bias_add_dev(void* output, const void* bias, int M, int N, void* stream) {
+    if (!output || !bias) return VV_ERR_NULL_PTR;
+    if (M < 0 || N < 0) return VV_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return VV_OK;
+    return from_cuda(vvbk_bias_add(output, bias, M, N, stream));
+}
+
+vv_status_t vv_fp32_to_fp16_dev(const void* in_fp32, void* out_fp16, int n, void* stream) {
+    if (!in_fp32 || !out_fp16) return VV_ERR_NULL_PTR;
+    if (n < 0) return VV_ERR_INVALID_ARG;
+    if (n == 0) return VV_OK;
+    return from_cuda(vvbk_f32_to_f16(in_fp32, out_fp16, (size_t)n, stream));
+}
+
+vv_status_t vv_fp16_to_fp32_dev(const void* in_fp16, void* out_fp32, int n, void* stream) {
+    if (!in_fp16 || !out_fp32) return VV_ERR_NULL_PTR;
+    if (n < 0) return VV_ERR_INVALID_ARG;
+    if (n == 0) return VV_OK;
+    return from_cuda(vvbk_f16_to_f32(in_fp16, out_fp32, (size_t)n, stream));
+}
+
+/* ------------------------------------------------------------------ group 2 */
+
+vv_status_t vvb_add_rmsnorm_dev(void* hidden_inout, const void* delta,
+                                const void* weight, void* normed_out,
+                                int rows, int hidden_size, float eps, void* stream) {
+    if (!hidden_inout || !weight || !normed_out) return VV_ERR_NULL_PTR;
+    if (rows < 0 || hidden_size < 0) return VV_ERR_INVALID_ARG;
+    if (rows == 0 || hidden_size == 0) return VV_OK;
+    /* With a delta the updated row is written back over hidden; without one
+     * hidden is only read. */
+    return from_cuda(vvbk_row_norm(hidden_inout, delta, NULL, 0,
+                                   delta ? hidden_inout : NULL, weight, normed_out,
+                                   rows, hidden_size, eps, stream));
+}
+
+vv_status_t vvb_embedding_rmsnorm_dev(const void* table, const int32_t* ids,
+                                      void* hidden_out, const void* weight,
+                                      void* normed_out, int rows, int hidden_size,
+                                      int vocab, float eps, void* stream) {
+    if (!table || !ids || !hidden_out) return VV_ERR_NULL_PTR;
+    if (normed_out && !weight) return VV_ERR_NULL_PTR;
+    if (rows < 0 || hidden_size < 0) return VV_ERR_INVALID_ARG;
+    if (rows == 0 || hidden_size == 0) return VV_OK;
+    return from_cuda(vvbk_row_norm(table, NULL, ids, vocab, hidden_out, weight, normed_out,
+                                   rows, hidden_size, eps, stream));
+}
+
+vv_status_t vvb_layer_chain_dev(const vvb_layer_chain_t* c, void* stream) {
+    if (!c) return VV_ERR_NULL_PTR;
+    if (c->rows < 0 || c->hidden_size < 0 || c->inter < 0) return VV_ERR_INVALID_ARG;
+    vv_status_t st = vvb_add_rmsnorm_dev(c->hidden, c->delta, c->norm_w, c->normed,
+                                         c->rows, c->hidden_size, c->eps, stream);
+    if (st != VV_OK) return st;
+    st = vvb_rope_qk_dev(c->q, c->k, c->rows, c->n_q_heads, c->n_kv_heads, c->head_dim,
+                         c->position_offset, NULL, c->theta, stream);
+    if (st != VV_OK) return st;
+    return vvb_swiglu_dev(c->gate, c->up, c->gate, (size_t)c->rows * (size_t)c->inter, stream);
+}
+
+/* ------------------------------------------------------------ introspection */
+
+const char* vvb_version(void) { return "vvb200 " VVB_VERSION " sm_100a"; }
+
+const char* vvb_status_string(int status) {
+    switch (status) {
+        case VV_OK: return "ok";
+        case VV_ERR_INVALID_ARG: return "invalid argument";
+        case VV_ERR_NULL_PTR: return "null pointer";
+        case VV_ERR_OUT_OF_MEMORY: return "out of host memory";
+        case VV_ERR_UNSUPPORTED: return "unsupported shape";
+        case VV_ERR_OVERFLOW: return "size overflow";
+        case VV_ERR_CUDA: return "CUDA runtime error";
+        case VV_ERR_CUDA_OOM: return "out of device memory";
+        case VV_ERR_CUDA_LAUNCH: return "kernel launch failed";
+        default: return "unknown status";
+    }
+}
+
+uint64_t vvb_launch_count(void) { return vvbk_launch_count(); }

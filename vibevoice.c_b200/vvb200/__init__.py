@@ -1,0 +1,244 @@
+"""vvb200 -- Python face of libvvb200 (ctypes over the C-ABI in include/vvb200.h).
+
+The functions carry the reference's op names and argument order
+(include/vibevoice/device.h:486-514): ``vv_rmsnorm_dev(input, weight, output,
+seq_len, hidden_size, eps, stream)`` and so on, and return the same status
+codes. A tensor argument may be a ``torch.Tensor`` on a CUDA device (its
+``data_ptr()`` is passed) or a raw integer device address; ``stream`` may be a
+``torch.cuda.Stream``, a raw ``cudaStream_t`` integer, or None for torch's
+current stream. torch is used for device memory and streams only -- every
+computation happens in the library's own kernels, and importing this package
+fails loudly if the library is missing: there is no fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libvvb200.so")
+
+VV_OK = 0
+VV_ERR_INVALID_ARG = -1
+VV_ERR_NULL_PTR = -2
+VV_ERR_OUT_OF_MEMORY = -3
+VV_ERR_UNSUPPORTED = -7
+VV_ERR_OVERFLOW = -8
+VV_ERR_CUDA = -100
+VV_ERR_CUDA_OOM = -101
+VV_ERR_CUDA_LAUNCH = -102
+
+
+class VvbError(RuntimeError):
+    def __init__(self, status: int, what: str):
+        self.status = status
+        super().__init__(f"{what}: status {status} ({status_string(status)})")
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} not found: build it with `make -C {os.path.dirname(_HERE)}` "
+            "(there is no fallback implementation)")
+    return C.CDLL(LIB_PATH)
+
+
+_lib = _load()
+
+_vp, _i, _f, _sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+
+
+class LayerChain(C.Structure):
+    """vvb_layer_chain_t (include/vvb200.h)."""
+    _fields_ = [
+        ("hidden", _vp), ("delta", _vp), ("norm_w", _vp), ("normed", _vp),
+        ("q", _vp), ("k", _vp), ("gate", _vp), ("up", _vp),
+        ("rows", _i), ("hidden_size", _i), ("n_q_heads", _i), ("n_kv_heads", _i),
+        ("head_dim", _i), ("inter", _i), ("position_offset", _i),
+        ("eps", _f), ("theta", _f),
+    ]
+
+
+# name -> (restype, argtypes): every symbol include/vvb200.h declares
+SIGNATURES = {
+    "vv_embedding_dev": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
+    "vv_rmsnorm_dev": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp]),
+    "vv_rope_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _f, _vp]),
+    "vv_swiglu_dev": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "vv_swiglu_fused_dev": (_i, [_vp, _vp, _i, _i, _vp]),
+    "vv_residual_add_dev": (_i, [_vp, _vp, _i, _vp]),
+    "vv_bias_add_dev": (_i, [_vp, _vp, _i, _i, _vp]),
+    "vv_fp32_to_fp16_dev": (_i, [_vp, _vp, _i, _vp]),
+    "vv_fp16_to_fp32_dev": (_i, [_vp, _vp, _i, _vp]),
+    "vvb_add_rmsnorm_dev": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
+    "vvb_rope_qk_dev": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp]),
+    "vvb_embedding_rmsnorm_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
+    "vvb_swiglu_dev": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "vvb_residual_add_dev": (_i, [_vp, _vp, _sz, _vp]),
+    "vvb_layer_chain_dev": (_i, [C.POINTER(LayerChain), _vp]),
+    "vvb_shard_rows": (_i, [C.c_int64, _i, _i, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+    "vvb_host_ctx_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i]),
+    "vvb_host_ctx_destroy": (None, [_vp]),
+    "vvb_layer_chain_host": (_i, [_vp, C.POINTER(LayerChain)]),
+    "vvb_host_ctx_last_traffic": (None, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "vvb_host_ctx_last_ms": (C.c_float, [_vp]),
+    "vvb_version": (C.c_char_p, []),
+    "vvb_status_string": (C.c_char_p, [_i]),
+    "vvb_launch_count": (C.c_uint64, []),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(_lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def _ptr(t):
+    """Device address of a tensor argument (None -> NULL)."""
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    return t.data_ptr()
+
+
+def _stream(s):
+    if s is None:
+        import torch
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(s, int):
+        return s
+    return s.cuda_stream
+
+
+def version() -> str:
+    return _lib.vvb_version().decode()
+
+
+def status_string(status: int) -> str:
+    return _lib.vvb_status_string(int(status)).decode()
+
+
+def launch_count() -> int:
+    return int(_lib.vvb_launch_count())
+
+
+def check(status: int, what: str = "vvb200") -> None:
+    if status != VV_OK:
+        raise VvbError(status, what)
+
+
+# ------------------------------------------------------------------ group 1
+def vv_embedding_dev(table, ids, output, seq_len, hidden_size, stream=None) -> int:
+    return _lib.vv_embedding_dev(_ptr(table), _ptr(ids), _ptr(output), seq_len, hidden_size, _stream(stream))
+
+
+def vv_rmsnorm_dev(input, weight, output, seq_len, hidden_size, eps, stream=None) -> int:
+    return _lib.vv_rmsnorm_dev(_ptr(input), _ptr(weight), _ptr(output), seq_len, hidden_size, eps, _stream(stream))
+
+
+def vv_rope_dev(x, seq_len, n_heads, head_dim, position_offset, d_position, theta, stream=None) -> int:
+    return _lib.vv_rope_dev(_ptr(x), seq_len, n_heads, head_dim, position_offset, _ptr(d_position), theta,
+                            _stream(stream))
+
+
+def vv_swiglu_dev(gate, up, output, n_elements, stream=None) -> int:
+    return _lib.vv_swiglu_dev(_ptr(gate), _ptr(up), _ptr(output), n_elements, _stream(stream))
+
+
+def vv_swiglu_fused_dev(gate_up, output, rows, inter, stream=None) -> int:
+    return _lib.vv_swiglu_fused_dev(_ptr(gate_up), _ptr(output), rows, inter, _stream(stream))
+
+
+def vv_residual_add_dev(x, y, total, stream=None) -> int:
+    return _lib.vv_residual_add_dev(_ptr(x), _ptr(y), total, _stream(stream))
+
+
+def vv_bias_add_dev(output, bias, M, N, stream=None) -> int:
+    return _lib.vv_bias_add_dev(_ptr(output), _ptr(bias), M, N, _stream(stream))
+
+
+def vv_fp32_to_fp16_dev(in_fp32, out_fp16, n, stream=None) -> int:
+    return _lib.vv_fp32_to_fp16_dev(_ptr(in_fp32), _ptr(out_fp16), n, _stream(stream))
+
+
+def vv_fp16_to_fp32_dev(in_fp16, out_fp32, n, stream=None) -> int:
+    return _lib.vv_fp16_to_fp32_dev(_ptr(in_fp16), _ptr(out_fp32), n, _stream(stream))
+
+
+# ------------------------------------------------------------------ group 2
+def vvb_add_rmsnorm_dev(hidden_inout, delta, weight, normed_out, rows, hidden_size, eps, stream=None) -> int:
+    return _lib.vvb_add_rmsnorm_dev(_ptr(hidden_inout), _ptr(delta), _ptr(weight), _ptr(normed_out),
+                                    rows, hidden_size, eps, _stream(stream))
+
+
+def vvb_rope_qk_dev(q, k, rows, n_q_heads, n_kv_heads, head_dim, position_offset, d_position, theta,
+                    stream=None) -> int:
+    return _lib.vvb_rope_qk_dev(_ptr(q), _ptr(k), rows, n_q_heads, n_kv_heads, head_dim, position_offset,
+                                _ptr(d_position), theta, _stream(stream))
+
+
+def vvb_embedding_rmsnorm_dev(table, ids, hidden_out, weight, normed_out, rows, hidden_size, vocab, eps,
+                              stream=None) -> int:
+    return _lib.vvb_embedding_rmsnorm_dev(_ptr(table), _ptr(ids), _ptr(hidden_out), _ptr(weight),
+                                          _ptr(normed_out), rows, hidden_size, vocab, eps, _stream(stream))
+
+
+def vvb_swiglu_dev(gate, up, output, n_elements, stream=None) -> int:
+    return _lib.vvb_swiglu_dev(_ptr(gate), _ptr(up), _ptr(output), n_elements, _stream(stream))
+
+
+def vvb_residual_add_dev(x, y, total, stream=None) -> int:
+    return _lib.vvb_residual_add_dev(_ptr(x), _ptr(y), total, _stream(stream))
+
+
+def make_chain(hidden, delta, norm_w, normed, q, k, gate, up, rows, hidden_size, n_q_heads, n_kv_heads,
+               head_dim, inter, position_offset=0, eps=1e-6, theta=1e6) -> LayerChain:
+    """Fill a vvb_layer_chain_t from tensors (device tensors for
+    vvb_layer_chain_dev, pinned host tensors for HostPipeline.run)."""
+    return LayerChain(_ptr(hidden), _ptr(delta), _ptr(norm_w), _ptr(normed), _ptr(q), _ptr(k), _ptr(gate),
+                      _ptr(up), rows, hidden_size, n_q_heads, n_kv_heads, head_dim, inter, position_offset,
+                      eps, theta)
+
+
+def vvb_layer_chain_dev(chain: LayerChain, stream=None) -> int:
+    return _lib.vvb_layer_chain_dev(C.byref(chain), _stream(stream))
+
+
+def vvb_shard_rows(total_rows: int, parts: int, part: int):
+    """(first, count) of the contiguous row block that `part` of `parts` owns."""
+    first, count = C.c_int64(), C.c_int64()
+    check(_lib.vvb_shard_rows(total_rows, parts, part, C.byref(first), C.byref(count)), "vvb_shard_rows")
+    return first.value, count.value
+
+
+class HostPipeline:
+    """vvb_host_ctx_t: runs the layer chain on tensors that live in (pinned)
+    host memory, overlapping uploads, kernels and downloads slice by slice."""
+
+    def __init__(self, device, max_slice_rows, hidden_size, n_q_heads, n_kv_heads, head_dim, inter):
+        self._ctx = _vp()
+        check(_lib.vvb_host_ctx_create(C.byref(self._ctx), device, max_slice_rows, hidden_size, n_q_heads,
+                                       n_kv_heads, head_dim, inter), "vvb_host_ctx_create")
+
+    def run(self, chain: LayerChain) -> int:
+        return _lib.vvb_layer_chain_host(self._ctx, C.byref(chain))
+
+    def last_traffic(self):
+        a, b = C.c_uint64(), C.c_uint64()
+        _lib.vvb_host_ctx_last_traffic(self._ctx, C.byref(a), C.byref(b))
+        return a.value, b.value
+
+    def last_ms(self) -> float:
+        return float(_lib.vvb_host_ctx_last_ms(self._ctx))
+
+    def close(self):
+        if self._ctx:
+            _lib.vvb_host_ctx_destroy(self._ctx)
+            self._ctx = _vp()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
