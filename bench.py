@@ -186,11 +186,11 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus, scaling="strong"):
+def workload_config(n_gpus, scaling="strong", rows=T_TOTAL):
     return {
         "workload": "Qwen2-7B layer chain at long-prompt prefill: add+RMSNorm [T,3584], RoPE Q [T,28,128] K [T,4,128] "
                     "at positions 0..T-1, SwiGLU [T,18944] in place; T=14449, fp16 ~ N(0,1), seed 1",
-        "rows_total": T_TOTAL * (n_gpus if scaling == "weak" else 1),
+        "rows_total": rows * (n_gpus if scaling == "weak" else 1),
         "sharding": f"contiguous token rows over {n_gpus} GPU(s), no collective",
         "eps": EPS, "theta": THETA,
         "l2": "inputs larger than L2: every rank's working set exceeds the 126 MB L2 and each pass streams it once",
@@ -231,7 +231,7 @@ def run_native(args):
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return float(t.item())
 
-    total_rows = T_TOTAL * (world if args.scaling == "weak" else 1)
+    total_rows = args.rows * (world if args.scaling == "weak" else 1)
     first, rows = vv.vvb_shard_rows(total_rows, world, rank)
 
     # The same seeded tensors on every rank count; each rank draws its own rows
@@ -310,6 +310,21 @@ def run_native(args):
     clocks = sampler.stop(t_region0, t_region1) if sampler else None
 
     # ---- e2e: host buffers through the pipeline API, copies inside the timed region
+    if args.no_e2e:
+        e2e_line = None
+    else:
+        e2e_line = run_e2e(args, vv, torch, (h0, d, w, q, k, g0, up), rows, first, local, total_rows,
+                           barrier, reduce_max, reduce_sum)
+
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    emit(args, world, total_rows, ms_total, ms_total_b, per, launches_all, clocks, e2e_line)
+
+
+def run_e2e(args, vv, torch, tensors, rows, first, local, total_rows, barrier, reduce_max, reduce_sum):
+    h0, d, w, q, k, g0, up = tensors
     pin = lambda t: t.cpu().pin_memory()
     hh, hd_, hw, hq, hk, hg, hu = (pin(t) for t in (h0, d, w, q, k, g0, up))
     hn = torch.empty_like(hh).pin_memory()
@@ -330,12 +345,14 @@ def run_native(args):
     e2e_wall_ms = reduce_max(wall_ms)
     h2d_all, d2h_all = int(reduce_sum(float(h2d))), int(reduce_sum(float(d2h)))
     pipe.close()
+    return {"value": total_rows * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
+            "h2d_bytes_per_step": h2d_all, "d2h_bytes_per_step": d2h_all, "steps": e2e_steps,
+            "ms_per_step": e2e_ms / e2e_steps, "wall_ms_per_step": e2e_wall_ms / e2e_steps,
+            "api": "vvb_layer_chain_host (pinned host tensors; uploads, kernels and downloads pipelined in "
+                   f"{args.slice_rows}-row slices)"}
 
-    if world > 1:
-        dist.destroy_process_group()
-    if rank != 0:
-        return
 
+def emit(args, world, total_rows, ms_total, ms_total_b, per, launches_all, clocks, e2e_line):
     peak, peak_kind = measured_hbm_peak()
     rows_max = -(-total_rows // world)       # the slowest rank holds ceil(T/N) rows
     kernels = {}
@@ -350,7 +367,7 @@ def run_native(args):
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": args.scaling,
         "vs_baseline": None, "dtype": "f16 storage, f32 arithmetic (f64 sum of squares)", "data": "synthetic",
-        "config": workload_config(world, args.scaling),
+        "config": workload_config(world, args.scaling, args.rows),
         "chain_GB/s_per_gpu": BYTES_CHAIN * rows_max / (ms_total / args.steps * 1e-3) / 1e9,
         "roofline": {"bound": "hbm", "kernel": top, "achieved": kernels[top]["GB/s"], "peak": peak, "unit": "GB/s",
                      "frac": kernels[top]["GB/s"] / peak, "peak_kind": "of " + peak_kind,
@@ -359,11 +376,7 @@ def run_native(args):
                                "a second pass of the same workload; ms_per_step_with_events = "
                                f"{ms_total_b / args.steps:.4f}"},
         "kernels": kernels,
-        "e2e": {"value": total_rows * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
-                "h2d_bytes_per_step": h2d_all, "d2h_bytes_per_step": d2h_all, "steps": e2e_steps,
-                "ms_per_step": e2e_ms / e2e_steps, "wall_ms_per_step": e2e_wall_ms / e2e_steps,
-                "api": "vvb_layer_chain_host (pinned host tensors; uploads, kernels and downloads pipelined in "
-                       f"{args.slice_rows}-row slices)"},
+        "e2e": e2e_line,
         "gpu_launches": launches_all,
         "clocks": clocks,
     }
@@ -400,6 +413,9 @@ def main():
     ap.add_argument("--slice-rows", type=int, default=1024, help="rows per slice of the host-buffer pipeline")
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
+    ap.add_argument("--rows", type=int, default=T_TOTAL,
+                    help="token rows in total (default: the named config's 14449; smaller for profiler captures)")
     ap.add_argument("--cpu-baseline-worker", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
 
