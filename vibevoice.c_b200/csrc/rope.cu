@@ -5,13 +5,14 @@
  * Layout: x[rows, n_heads, head_dim] FP16; pairs (i, i + head_dim/2)
  * (rotate_half). The work of one row is (n_q + n_kv) heads x head_dim/16
  * "items"; an item is one 16-byte vector from the low half of a head and its
- * partner vector from the high half (8 pairs). A CTA of 256 threads takes a
- * tile of up to 1024 items -- four rows of the 7B shape (32 heads x 8 items) --
- * so every thread first puts eight 16-byte loads in flight, then the CTA
- * computes the tile's cos/sin table ONCE per (row, frequency) into shared
- * memory while those loads travel, and every head of the row reuses it. (The
- * reference recomputes powf/cosf/sinf for each of the 32 heads:
- * src/cuda/rope.cu:54-57.)
+ * partner vector from the high half (8 pairs). A thread owns ONE item column
+ * (head, vector) and walks up to four rows of it, so all index arithmetic is
+ * done once per thread and the row loop only adds a stride. A CTA of 256
+ * threads covers 256 columns -- the whole 7B row (32 heads x 8 vectors) -- of
+ * up to four rows: every thread first puts eight 16-byte loads in flight, then
+ * the CTA computes its cos/sin table ONCE per (row, frequency) into shared
+ * memory while the loads travel, and all 32 heads reuse it. (The reference
+ * recomputes powf/cosf/sinf for each head: src/cuda/rope.cu:54-57.)
  *
  * Arithmetic, chosen to land on the reference CPU kernel's bits
  * (src/cpu/cpu_kernels.c:1466-1474):
@@ -20,9 +21,11 @@
  *            freq_i is several FP16 ulps in the result at positions ~1e4, and
  *            a device powf is not bit-identical to glibc's;
  *   ang      (float)pos * freq_i, one float multiply, as on the CPU;
- *   cos/sin  evaluated in DOUBLE on the float angle and rounded to float: the
- *            correctly rounded value, which is what glibc's cosf/sinf return
- *            in all but rare cases (64 evaluations per row, negligible);
+ *   cos/sin  evaluated in DOUBLE on the float angle (three-term Cody-Waite
+ *            reduction by pi/2 with fused multiply-adds, then Taylor
+ *            polynomials on [-pi/4, pi/4], absolute error < 1e-14) and rounded
+ *            to float: the correctly rounded value, which is what glibc's
+ *            cosf/sinf return in all but rare cases;
  *   rotate   a*c - b*s and a*s + b*c with four separately rounded products
  *            (no FMA contraction, as in the reference's default CPU build).
  * No global or file-scope state: the launch is re-entrant and capturable, and
@@ -32,100 +35,142 @@
 #include "vvb_launch.h"
 
 #include <atomic>
+#ifdef VVB_TUNING
+#include <cstdlib>
+#endif
 
 namespace vvb {
 
 extern std::atomic<uint64_t> g_launches;
 
 constexpr int kRopeThreads = 256;
-constexpr int kRopeItemsPerThread = 4;
-constexpr int kRopeTileItems = kRopeThreads * kRopeItemsPerThread; /* 1024 */
-constexpr int kRopeTableEntries = 1024;                            /* rows_per_tile * half <= this */
+constexpr int kRopeMaxRowsPerThread = 4;
+constexpr int kRopeTableEntries = 1024;   /* rows_per_cta * half <= this */
 
 struct RopeArgs {
     vec16* q;
     vec16* k;
     const int* d_position;
     int rows, n_q, n_kv;
-    int half;            /* head_dim / 2 */
-    int hvn;             /* half / 8: vectors per half head */
-    int items_per_row;   /* (n_q + n_kv) * hvn */
-    int rows_per_tile;   /* R */
-    int chunk_items;     /* items of one row a CTA covers (== items_per_row unless the row is split) */
+    int half;              /* head_dim / 2 */
+    int hvn;               /* half / 8: vectors per half head */
+    int items_per_row;     /* (n_q + n_kv) * hvn */
+    int cols_per_cta;      /* min(items_per_row, 256) */
+    int row_slots;         /* 256 / cols_per_cta: rows a CTA touches per pass */
+    int passes;            /* rows per thread, 1..4 */
     int position_offset;
     float inv_freq[VVB_ROPE_MAX_HALF];
 };
 
-__device__ __forceinline__ vec16* item_ptr(const RopeArgs& a, int row, int c) {
-    const int head = c / a.hvn;
-    const int vec = c - head * a.hvn;
-    const size_t vecs_per_head = (size_t)(2 * a.hvn);
-    if (head < a.n_q)
-        return a.q + ((size_t)row * (size_t)a.n_q + (size_t)head) * vecs_per_head + vec;
-    return a.k + ((size_t)row * (size_t)a.n_kv + (size_t)(head - a.n_q)) * vecs_per_head + vec;
+/* sin and cos of a float angle, evaluated in double and rounded to float.
+ * k = nearest integer to x*2/pi (|k| < 2^31 for every |x| <= 2^31);
+ * r = x - k*pi/2 with pi/2 = P1 + P2 + P3, each product exact inside the FMA. */
+__device__ __forceinline__ void sincos_f64(float angle, float* s_out, float* c_out) {
+    const double x = (double)angle;
+    const double kShift = 6755399441055744.0;                 /* 1.5 * 2^52 */
+    const double t = fma(x, 0.63661977236758134308, kShift);  /* 2/pi */
+    const int q = __double2loint(t);
+    const double k = t - kShift;
+    double r = fma(-k, 1.57079632679489655800e+00, x);
+    r = fma(-k, 6.12323399573676603587e-17, r);
+    r = fma(-k, -1.49738490485916983294e-33, r);
+    const double r2 = r * r;
+    /* sin r = r + r^3 * (-1/3! + r^2/5! - ... + r^12/15!) */
+    double ps = 1.0 / 1307674368000.0;
+    ps = fma(ps, r2, -1.0 / 6227020800.0);
+    ps = fma(ps, r2, 1.0 / 39916800.0);
+    ps = fma(ps, r2, -1.0 / 362880.0);
+    ps = fma(ps, r2, 1.0 / 5040.0);
+    ps = fma(ps, r2, -1.0 / 120.0);
+    ps = fma(ps, r2, 1.0 / 6.0);
+    const double sn = fma(-ps * r2, r, r);
+    /* cos r = 1 - r^2/2! + r^4/4! - ... + r^16/16! */
+    double pc = 1.0 / 20922789888000.0;
+    pc = fma(pc, r2, -1.0 / 87178291200.0);
+    pc = fma(pc, r2, 1.0 / 479001600.0);
+    pc = fma(pc, r2, -1.0 / 3628800.0);
+    pc = fma(pc, r2, 1.0 / 40320.0);
+    pc = fma(pc, r2, -1.0 / 720.0);
+    pc = fma(pc, r2, 1.0 / 24.0);
+    pc = fma(pc, r2, -0.5);
+    const double cs = fma(pc, r2, 1.0);
+    const float sf = (float)sn, cf = (float)cs;
+    const float s1 = (q & 1) ? cf : sf;      /* quadrant: 0:(s,c) 1:(c,-s) 2:(-s,-c) 3:(-c,s) */
+    const float c1 = (q & 1) ? sf : cf;
+    *s_out = (q & 2) ? -s1 : s1;
+    *c_out = ((q + 1) & 2) ? -c1 : c1;
 }
 
-__global__ void __launch_bounds__(kRopeThreads)
+__global__ void __launch_bounds__(kRopeThreads, 4)
 rope_tile_kernel(const __grid_constant__ RopeArgs a) {
     __shared__ __align__(16) float cos_s[kRopeTableEntries];
     __shared__ __align__(16) float sin_s[kRopeTableEntries];
 
     const int t = threadIdx.x;
-    const int row0 = blockIdx.x * a.rows_per_tile;
-    const int c0 = blockIdx.y * a.chunk_items;
-    const int nrows = min(a.rows_per_tile, a.rows - row0);
-    const int ncols = min(a.chunk_items, a.items_per_row - c0);
-    const int nitems = nrows * ncols;
+    const int rows_per_cta = a.row_slots * a.passes;
+    const int row0 = blockIdx.x * rows_per_cta;
+    const int nrows = min(rows_per_cta, a.rows - row0);
+
+    /* This thread's column, fixed for all its rows. */
+    const int slot = t / a.cols_per_cta;
+    const int cl = t - slot * a.cols_per_cta;
+    const int c = blockIdx.y * kRopeThreads + cl;
+    const bool col_ok = (slot < a.row_slots) && (c < a.items_per_row);
+    const int head = c / a.hvn;
+    const int vec = c - head * a.hvn;
+    const size_t vph = (size_t)(2 * a.hvn);               /* vectors per head */
+    vec16* base;
+    size_t row_stride;                                     /* vectors between consecutive rows */
+    if (head < a.n_q) {
+        row_stride = (size_t)a.n_q * vph;
+        base = a.q + (size_t)head * vph + vec;
+    } else {
+        row_stride = (size_t)a.n_kv * vph;
+        base = a.k + (size_t)(head - a.n_q) * vph + vec;
+    }
 
     /* Phase A: put this thread's loads in flight. */
-    vec16 lo[kRopeItemsPerThread], hi[kRopeItemsPerThread];
-    vec16* ptr[kRopeItemsPerThread];
-    int tab[kRopeItemsPerThread];   /* index of the item's first cos/sin entry */
+    vec16 lo[kRopeMaxRowsPerThread], hi[kRopeMaxRowsPerThread];
+    vec16* ptr[kRopeMaxRowsPerThread];
 #pragma unroll
-    for (int m = 0; m < kRopeItemsPerThread; m++) {
-        const int it = t + m * kRopeThreads;
+    for (int m = 0; m < kRopeMaxRowsPerThread; m++) {
+        const int rl = slot + m * a.row_slots;
         ptr[m] = nullptr;
-        tab[m] = 0;
-        if (it < nitems) {
-            const int rl = it / ncols;
-            const int c = c0 + (it - rl * ncols);
-            vec16* p = item_ptr(a, row0 + rl, c);
+        if (col_ok && m < a.passes && rl < nrows) {
+            vec16* p = base + (size_t)(row0 + rl) * row_stride;
             ptr[m] = p;
-            tab[m] = rl * a.half + (c % a.hvn) * 8;
             lo[m] = ld_stream(p);
             hi[m] = ld_stream(p + a.hvn);
         }
     }
 
-    /* Phase B: the tile's cos/sin, once per (row, frequency). */
+    /* Phase B: the CTA's cos/sin, once per (row, frequency). */
     const int pos0 = (a.d_position != nullptr ? *a.d_position : a.position_offset) + row0;
     for (int e = t; e < nrows * a.half; e += kRopeThreads) {
         const int rl = e / a.half;
         const int i = e - rl * a.half;
         const float ang = __fmul_rn((float)(pos0 + rl), a.inv_freq[i]);
-        double s, c;
-        sincos((double)ang, &s, &c);
-        cos_s[e] = (float)c;
-        sin_s[e] = (float)s;
+        sincos_f64(ang, &sin_s[e], &cos_s[e]);
     }
     __syncthreads();
 
     /* Phase C: rotate and store. */
 #pragma unroll
-    for (int m = 0; m < kRopeItemsPerThread; m++) {
+    for (int m = 0; m < kRopeMaxRowsPerThread; m++) {
         if (ptr[m] == nullptr) continue;
-        float x0[8], x1[8], c[8], s[8];
+        const int tab = (slot + m * a.row_slots) * a.half + vec * 8;
+        float x0[8], x1[8], c8[8], s8[8];
         unpack8(lo[m], x0);
         unpack8(hi[m], x1);
-        *reinterpret_cast<float4*>(&c[0]) = *reinterpret_cast<const float4*>(&cos_s[tab[m]]);
-        *reinterpret_cast<float4*>(&c[4]) = *reinterpret_cast<const float4*>(&cos_s[tab[m] + 4]);
-        *reinterpret_cast<float4*>(&s[0]) = *reinterpret_cast<const float4*>(&sin_s[tab[m]]);
-        *reinterpret_cast<float4*>(&s[4]) = *reinterpret_cast<const float4*>(&sin_s[tab[m] + 4]);
+        *reinterpret_cast<float4*>(&c8[0]) = *reinterpret_cast<const float4*>(&cos_s[tab]);
+        *reinterpret_cast<float4*>(&c8[4]) = *reinterpret_cast<const float4*>(&cos_s[tab + 4]);
+        *reinterpret_cast<float4*>(&s8[0]) = *reinterpret_cast<const float4*>(&sin_s[tab]);
+        *reinterpret_cast<float4*>(&s8[4]) = *reinterpret_cast<const float4*>(&sin_s[tab + 4]);
         float y0[8], y1[8];
 #pragma unroll
         for (int e = 0; e < 8; e++) {
-            y0[e] = __fsub_rn(__fmul_rn(x0[e], c[e]), __fmul_rn(x1[e], s[e]));
-            y1[e] = __fadd_rn(__fmul_rn(x0[e], s[e]), __fmul_rn(x1[e], c[e]));
+            y0[e] = __fsub_rn(__fmul_rn(x0[e], c8[e]), __fmul_rn(x1[e], s8[e]));
+            y1[e] = __fadd_rn(__fmul_rn(x0[e], s8[e]), __fmul_rn(x1[e], c8[e]));
         }
         st_stream(ptr[m], pack8(y0));
         st_stream(ptr[m] + a.hvn, pack8(y1));
@@ -156,9 +201,8 @@ rope_scalar_kernel(const __grid_constant__ RopeScalarArgs a) {
             ? a.q + ((size_t)row * (size_t)a.n_q + (size_t)head) * (size_t)a.head_dim
             : a.k + ((size_t)row * (size_t)a.n_kv + (size_t)(head - a.n_q)) * (size_t)a.head_dim;
         const float ang = __fmul_rn((float)(pos_base + row), a.inv_freq[i]);
-        double sd, cd;
-        sincos((double)ang, &sd, &cd);
-        const float c = (float)cd, s = (float)sd;
+        float s, c;
+        sincos_f64(ang, &s, &c);
         const float x0 = __half2float(v[i]), x1 = __half2float(v[i + a.half]);
         v[i] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
         v[i + a.half] = __float2half_rn(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
@@ -192,21 +236,24 @@ extern "C" int vvbk_rope(void* q, void* k, int rows, int n_q_heads, int n_kv_hea
         a.items_per_row = heads * a.hvn;
         a.position_offset = position_offset;
         for (int i = 0; i < half; i++) a.inv_freq[i] = inv_freq[i];
-        unsigned grid_y = 1;
-        if (a.items_per_row <= kRopeTileItems) {
-            int r = kRopeTileItems / a.items_per_row;
-            const int table_rows = kRopeTableEntries / half;
-            if (r > table_rows) r = table_rows;
-            if (r > rows) r = rows;
-            a.rows_per_tile = r;
-            a.chunk_items = a.items_per_row;
-        } else {
-            a.rows_per_tile = 1;
-            a.chunk_items = kRopeTileItems;
-            grid_y = (unsigned)((a.items_per_row + kRopeTileItems - 1) / kRopeTileItems);
+        a.cols_per_cta = a.items_per_row < kRopeThreads ? a.items_per_row : kRopeThreads;
+        a.row_slots = kRopeThreads / a.cols_per_cta;
+        /* rows per CTA = row_slots * passes, bounded by the cos/sin table */
+        int passes = kRopeTableEntries / (half * a.row_slots);
+        if (passes > kRopeMaxRowsPerThread) passes = kRopeMaxRowsPerThread;
+#ifdef VVB_TUNING
+        if (const char* e = getenv("VVB_TUNE_ROPE_PASSES")) { int p = atoi(e); if (p >= 1 && p < passes) passes = p; }
+#endif
+        if (passes < 1) {                       /* narrow rows of a wide head: fewer row slots */
+            a.row_slots = kRopeTableEntries / half;
+            passes = 1;
         }
-        dim3 grid((unsigned)((rows + a.rows_per_tile - 1) / a.rows_per_tile), grid_y);
-        rope_tile_kernel<<<grid, kRopeThreads, 0, s>>>(a);
+        a.passes = passes;
+        const int rows_per_cta = a.row_slots * a.passes;
+        const unsigned gx = (unsigned)((rows + rows_per_cta - 1) / rows_per_cta);
+        const unsigned gy = (unsigned)((a.items_per_row + kRopeThreads - 1) / kRopeThreads);
+        if (gy > 65535u) return (int)cudaErrorInvalidValue;
+        rope_tile_kernel<<<dim3(gx, gy), kRopeThreads, 0, s>>>(a);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return (int)cudaGetLastError();
     }

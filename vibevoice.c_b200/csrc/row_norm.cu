@@ -2,20 +2,20 @@
  * row_norm.cu -- the row kernels: RMSNorm, residual add + RMSNorm, embedding
  * gather (+ RMSNorm). sm_100a, HBM-bound, no tensor cores.
  *
- * One row of 3584 halves is 448 16-byte vectors. Two shapes of kernel:
+ *   row_norm_cta_kernel<VPT>   one CTA per row, VPT 16-byte vectors per thread
+ *       held in registers, gamma straight into registers beside the row loads
+ *       (it stays L1/L2-resident), warp-shuffle + one shared-memory step for
+ *       the sum of squares. The grid is one CTA per row and nothing loops, so
+ *       the hardware's CTA scheduler balances rows over SMs and the tail is one
+ *       row long. Measured on B200 for 3584-wide rows: 128 threads x 4 vectors
+ *       (9 rows resident per SM) streams at the copy rate; more bytes per
+ *       thread (a warp per row, 14 vectors per lane) or fewer (448 threads x 1)
+ *       both lose 15-25 % when there are many rows.
+ *   row_norm_generic_kernel    any hidden size / alignment, scalar halves.
+ *   gather_rows_vec_kernel     the plain embedding gather.
  *
- *   row_norm_warp_kernel<VPT>   one WARP per row, VPT vectors per lane held in
- *       registers, no block-wide barrier; gamma staged once per CTA into
- *       shared memory with cp.async and reused for every row the CTA handles.
- *       Used when there are enough rows to fill the machine with warps
- *       (prefill). A lane has up to 2*VPT 16-byte loads in flight.
- *   row_norm_cta_kernel<VPT>    one CTA per row, one to four vectors per
- *       thread, gamma straight into registers next to the row loads so a
- *       single row costs one DRAM round trip (decode, short slices).
- *   row_norm_generic_kernel     any hidden size / alignment, scalar halves.
- *
- * Arithmetic (identical in all three; mirrors the reference's CPU kernels so
- * results agree bit for bit except on rounding-boundary accidents):
+ * Arithmetic (identical in all; mirrors the reference's CPU kernels so results
+ * agree bit for bit except on rounding-boundary accidents):
  *   h'  = f16(float(h) + float(delta))          src/cuda/conv_vae.cu:29-31
  *   ss  = sum over the ROUNDED h' of h'*h' in double
  *                                               src/cpu/cpu_kernels.c:1444-1445
@@ -33,6 +33,9 @@
 #include "vvb_launch.h"
 
 #include <atomic>
+#ifdef VVB_TUNING
+#include <cstdlib>
+#endif
 
 namespace vvb {
 
@@ -44,7 +47,7 @@ struct RowNormArgs {
     const int32_t* ids;   /* may be null */
     vec16* row_out;       /* may be null */
     const vec16* weight;
-    vec16* normed;        /* never null in the norm kernels */
+    vec16* normed;        /* never null in the norm kernel */
     int rows;
     int nvec;             /* hidden / 8 */
     int hidden;
@@ -52,28 +55,40 @@ struct RowNormArgs {
     float eps;
 };
 
-__device__ __forceinline__ size_t source_row(const RowNormArgs& a, int row) {
-    if (a.ids == nullptr) return (size_t)row;
-    int id = a.ids[row];
-    if (a.vocab > 0) id = min(max(id, 0), a.vocab - 1);
-    return (size_t)id;
-}
-
 __device__ __forceinline__ float inv_rms(double ss, int hidden, float eps) {
     const float mean = (float)(ss / (double)hidden);
     return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
 }
 
-/* Loads this thread's vectors of one row, applies the residual add, stores
- * the updated row, and returns the thread's partial sum of squares. hv[] is
- * left holding the (rounded) row. t = index within the group of G threads. */
+__device__ __forceinline__ vec16 scale_row_vec(const vec16& h, const vec16& w, float inv) {
+    float f[8], g[8];
+    unpack8(h, f);
+    unpack8(w, g);
+#pragma unroll
+    for (int e = 0; e < 8; e++) f[e] = __fmul_rn(__fmul_rn(f[e], inv), g[e]);
+    return pack8(f);
+}
+
+/* ----------------------------------------------------------------- CTA/row */
 template <int VPT>
-__device__ __forceinline__ double load_add_square(const RowNormArgs& a, int row, int t, int G,
-                                                   vec16 (&hv)[VPT]) {
+__global__ void __launch_bounds__(1024)
+row_norm_cta_kernel(const RowNormArgs a) {
+    __shared__ double red[32];
+    const int t = threadIdx.x, G = blockDim.x;
+    const int row = blockIdx.x;
     const size_t roff = (size_t)row * (size_t)a.nvec;
-    const vec16* sp = a.src + source_row(a, row) * (size_t)a.nvec;
-    vec16 dv[VPT];
+
+    size_t srow = (size_t)row;
+    if (a.ids != nullptr) {
+        int id = a.ids[row];
+        if (a.vocab > 0) id = min(max(id, 0), a.vocab - 1);
+        srow = (size_t)id;
+    }
+    const vec16* sp = a.src + srow * (size_t)a.nvec;
     const bool has_delta = (a.delta != nullptr);
+
+    /* Every load of the row, the addend and gamma goes out before any is used. */
+    vec16 hv[VPT], dv[VPT], wv[VPT];
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
         const int v = t + j * G;
@@ -87,6 +102,12 @@ __device__ __forceinline__ double load_add_square(const RowNormArgs& a, int row,
             dv[j] = (v < a.nvec) ? ld_stream(dp + v) : make_uint4(0, 0, 0, 0);
         }
     }
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        const int v = t + j * G;
+        wv[j] = (v < a.nvec) ? __ldg(a.weight + v) : make_uint4(0, 0, 0, 0);
+    }
+
     double ss = 0.0;
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
@@ -111,102 +132,22 @@ __device__ __forceinline__ double load_add_square(const RowNormArgs& a, int row,
             if (v < a.nvec) st_stream(rp + v, hv[j]);
         }
     }
-    return ss;
-}
 
-__device__ __forceinline__ vec16 scale_row_vec(const vec16& h, const vec16& w, float inv) {
-    float f[8], g[8];
-    unpack8(h, f);
-    unpack8(w, g);
-#pragma unroll
-    for (int e = 0; e < 8; e++) f[e] = __fmul_rn(__fmul_rn(f[e], inv), g[e]);
-    return pack8(f);
-}
+    ss = warp_sum(ss);
+    if ((t & 31) == 0) red[t >> 5] = ss;
+    __syncthreads();
+    /* every thread adds the warp sums in the same order: one barrier, and all
+     * threads hold the same total */
+    ss = 0.0;
+    const int nwarps = G >> 5;
+    for (int w = 0; w < nwarps; w++) ss += red[w];
+    const float inv = inv_rms(ss, a.hidden, a.eps);
 
-/* ---------------------------------------------------------------- warp/row */
-constexpr int kWarpKernelThreads = 128;
-
-template <int VPT>
-__device__ __forceinline__ void store_normed_warp(const RowNormArgs& a, int row, int lane,
-                                                  const vec16 (&hv)[VPT], const vec16* gamma, float inv) {
-    vec16* np_ = a.normed + (size_t)row * (size_t)a.nvec;
-#pragma unroll
-    for (int j = 0; j < VPT; j++) {
-        const int v = lane + j * 32;
-        if (v < a.nvec) st_stream(np_ + v, scale_row_vec(hv[j], gamma[v], inv));
-    }
-}
-
-template <int VPT>
-__global__ void __launch_bounds__(kWarpKernelThreads)
-row_norm_warp_kernel(const RowNormArgs a) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    vec16* gamma = reinterpret_cast<vec16*>(smem_raw);
-    for (int v = threadIdx.x; v < a.nvec; v += kWarpKernelThreads) cp_async16(gamma + v, a.weight + v);
-    cp_async_commit();
-
-    const int lane = threadIdx.x & 31;
-    const int warps_per_cta = kWarpKernelThreads / 32;
-    int row = blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
-    const int warp_stride = gridDim.x * warps_per_cta;
-
-    /* First row: its loads are issued before the CTA waits for gamma, so the
-     * staging copy and the row loads share one memory round trip. */
-    {
-        vec16 hv[VPT];
-        float inv = 0.0f;
-        const bool have = row < a.rows;
-        if (have) {
-            double ss = load_add_square<VPT>(a, row, lane, 32, hv);
-            inv = inv_rms(warp_sum(ss), a.hidden, a.eps);
-        }
-        cp_async_wait_all();
-        __syncthreads();
-        if (have) store_normed_warp<VPT>(a, row, lane, hv, gamma, inv);
-    }
-    for (row += warp_stride; row < a.rows; row += warp_stride) {
-        vec16 hv[VPT];
-        double ss = load_add_square<VPT>(a, row, lane, 32, hv);
-        const float inv = inv_rms(warp_sum(ss), a.hidden, a.eps);
-        store_normed_warp<VPT>(a, row, lane, hv, gamma, inv);
-    }
-}
-
-/* ----------------------------------------------------------------- CTA/row */
-template <int VPT>
-__global__ void __launch_bounds__(512)
-row_norm_cta_kernel(const RowNormArgs a) {
-    __shared__ double red[2][32];
-    __shared__ float inv_s[2];
-    const int t = threadIdx.x, G = blockDim.x;
-    const int lane = t & 31, warp = t >> 5, nwarps = G >> 5;
-
-    vec16 wv[VPT];
+    vec16* np_ = a.normed + roff;
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
         const int v = t + j * G;
-        wv[j] = (v < a.nvec) ? __ldg(a.weight + v) : make_uint4(0, 0, 0, 0);
-    }
-    int parity = 0;
-    for (int row = blockIdx.x; row < a.rows; row += gridDim.x, parity ^= 1) {
-        vec16 hv[VPT];
-        double ss = load_add_square<VPT>(a, row, t, G, hv);
-        ss = warp_sum(ss);
-        if (lane == 0) red[parity][warp] = ss;
-        __syncthreads();
-        if (warp == 0) {
-            double s = (lane < nwarps) ? red[parity][lane] : 0.0;
-            s = warp_sum(s);
-            if (lane == 0) inv_s[parity] = inv_rms(s, a.hidden, a.eps);
-        }
-        __syncthreads();
-        const float inv = inv_s[parity];
-        vec16* np_ = a.normed + (size_t)row * (size_t)a.nvec;
-#pragma unroll
-        for (int j = 0; j < VPT; j++) {
-            const int v = t + j * G;
-            if (v < a.nvec) st_stream(np_ + v, scale_row_vec(hv[j], wv[j], inv));
-        }
+        if (v < a.nvec) st_stream(np_ + v, scale_row_vec(hv[j], wv[j], inv));
     }
 }
 
@@ -236,8 +177,6 @@ row_norm_generic_kernel(const RowNormGenericArgs a) {
         }
         const __half* sp = a.src + srow * (size_t)a.hidden;
         const size_t roff = (size_t)row * (size_t)a.hidden;
-        /* Where the rounded row can be re-read in pass 2: the updated hidden
-         * row if one is written, else the source itself (no add happened). */
         double ss = 0.0;
         for (int i = t; i < a.hidden; i += 256) {
             float f = __half2float(sp[i]);
@@ -279,24 +218,23 @@ row_norm_generic_kernel(const RowNormGenericArgs a) {
 __global__ void __launch_bounds__(256)
 gather_rows_vec_kernel(const vec16* __restrict__ table, const int32_t* __restrict__ ids,
                        vec16* __restrict__ out, int rows, int nvec, int vocab) {
-    /* Each CTA copies whole rows; 4 independent 16-byte loads per thread. */
-    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-        int id = ids[row];
-        if (vocab > 0) id = min(max(id, 0), vocab - 1);
-        const vec16* sp = table + (size_t)id * (size_t)nvec;
-        vec16* dp = out + (size_t)row * (size_t)nvec;
-        for (int v0 = threadIdx.x; v0 < nvec; v0 += 256 * 4) {
-            vec16 r[4];
+    /* One CTA per row; 4 independent 16-byte loads per thread per trip. */
+    const int row = blockIdx.x;
+    int id = ids[row];
+    if (vocab > 0) id = min(max(id, 0), vocab - 1);
+    const vec16* sp = table + (size_t)id * (size_t)nvec;
+    vec16* dp = out + (size_t)row * (size_t)nvec;
+    for (int v0 = threadIdx.x; v0 < nvec; v0 += blockDim.x * 4) {
+        vec16 r[4];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int v = v0 + j * 256;
-                if (v < nvec) r[j] = ld_stream(sp + v);
-            }
+        for (int j = 0; j < 4; j++) {
+            const int v = v0 + j * blockDim.x;
+            if (v < nvec) r[j] = ld_stream(sp + v);
+        }
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int v = v0 + j * 256;
-                if (v < nvec) st_stream(dp + v, r[j]);
-            }
+        for (int j = 0; j < 4; j++) {
+            const int v = v0 + j * blockDim.x;
+            if (v < nvec) st_stream(dp + v, r[j]);
         }
     }
 }
@@ -316,26 +254,18 @@ static int sm_count() {
     return cached_sms;
 }
 
-template <int VPT>
-static cudaError_t launch_warp(const RowNormArgs& a, cudaStream_t s) {
-    const int rows_per_cta = kWarpKernelThreads / 32;
-    const int ctas_needed = (a.rows + rows_per_cta - 1) / rows_per_cta;
-    const int resident = sm_count() * 4;
-    const int grid = ctas_needed < resident ? ctas_needed : resident;
-    const size_t smem = (size_t)a.nvec * sizeof(vec16);
-    row_norm_warp_kernel<VPT><<<grid, kWarpKernelThreads, smem, s>>>(a);
+static cudaError_t launch_cta(const RowNormArgs& a, int vpt, int threads, cudaStream_t s) {
+    switch (vpt) {
+        case 1: row_norm_cta_kernel<1><<<a.rows, threads, 0, s>>>(a); break;
+        case 2: row_norm_cta_kernel<2><<<a.rows, threads, 0, s>>>(a); break;
+        case 4: row_norm_cta_kernel<4><<<a.rows, threads, 0, s>>>(a); break;
+        default: return cudaErrorInvalidValue;
+    }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaGetLastError();
 }
 
-template <int VPT>
-static cudaError_t launch_cta(const RowNormArgs& a, int threads, cudaStream_t s) {
-    const int resident = sm_count() * (2048 / threads);
-    const int grid = a.rows < resident ? a.rows : resident;
-    row_norm_cta_kernel<VPT><<<grid, threads, 0, s>>>(a);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    return cudaGetLastError();
-}
+static int round_up_warp(int n) { return ((n + 31) / 32) * 32; }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -355,10 +285,10 @@ extern "C" int vvbk_row_norm(const void* src_rows, const void* delta, const int3
     if (normed == nullptr) {
         /* gather (or add) without a norm */
         if (ids != nullptr && delta == nullptr && vec_ok) {
-            const int resident = sm_count() * 8;
-            const int grid = rows < resident ? rows : resident;
-            gather_rows_vec_kernel<<<grid, 256, 0, s>>>((const vec16*)src_rows, ids, (vec16*)row_out,
-                                                        rows, nvec, vocab);
+            int threads = round_up_warp((nvec + 3) / 4);
+            if (threads > 256) threads = 256;
+            gather_rows_vec_kernel<<<rows, threads, 0, s>>>((const vec16*)src_rows, ids, (vec16*)row_out,
+                                                            rows, nvec, vocab);
             g_launches.fetch_add(1, std::memory_order_relaxed);
             return (int)cudaGetLastError();
         }
@@ -370,27 +300,22 @@ extern "C" int vvbk_row_norm(const void* src_rows, const void* delta, const int3
         return (int)cudaGetLastError();
     }
 
-    if (vec_ok && nvec <= 2048) {
+    if (vec_ok && nvec <= 4096) {
         RowNormArgs a{(const vec16*)src_rows, (const vec16*)delta, ids, (vec16*)row_out,
                       (const vec16*)weight, (vec16*)normed, rows, nvec, hidden, vocab, eps};
-        /* Enough rows to give every SM several warps of its own: warp per row. */
-        const bool many_rows = rows >= sm_count() * 8;
-        if (many_rows && nvec <= 512) {
-            const int vpt = (nvec + 31) / 32;
-            if (vpt <= 1) return (int)launch_warp<1>(a, s);
-            if (vpt <= 2) return (int)launch_warp<2>(a, s);
-            if (vpt <= 4) return (int)launch_warp<4>(a, s);
-            if (vpt <= 7) return (int)launch_warp<7>(a, s);
-            if (vpt <= 8) return (int)launch_warp<8>(a, s);
-            if (vpt <= 14) return (int)launch_warp<14>(a, s);
-            return (int)launch_warp<16>(a, s);
+        /* A quarter of the row's vectors per thread (128 threads x 4 for a
+         * 3584-wide row): measured fastest from one row to fourteen thousand. */
+        int threads = round_up_warp((nvec + 3) / 4);
+        if (threads > 1024) threads = 1024;
+        int vpt = (nvec + threads - 1) / threads;
+        if (vpt == 3) vpt = 4;
+#ifdef VVB_TUNING
+        if (const char* e = getenv("VVB_TUNE_ROWNORM_VPT")) {
+            vpt = atoi(e);
+            threads = round_up_warp((nvec + vpt - 1) / vpt);
         }
-        int threads = ((nvec + 31) / 32) * 32;
-        if (threads > 512) threads = 512;
-        const int vpt = (nvec + threads - 1) / threads;
-        if (vpt <= 1) return (int)launch_cta<1>(a, threads, s);
-        if (vpt <= 2) return (int)launch_cta<2>(a, threads, s);
-        return (int)launch_cta<4>(a, threads, s);
+#endif
+        return (int)launch_cta(a, vpt, threads, s);
     }
 
     /* Scalar path. With a delta, the rounded sum must be re-readable in the

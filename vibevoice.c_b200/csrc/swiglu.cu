@@ -3,9 +3,11 @@
  *
  * Two reads and one write per element and nothing reused: the kernel is a
  * pure HBM stream (113 664 bytes per token of the 7B model, 72 % of the whole
- * layer chain's traffic). Each thread issues kUnroll 16-byte loads from gate
- * and kUnroll from up before it touches any of them (128 bytes in flight per
- * thread), with the streaming cache operator on loads and stores. The
+ * layer chain's traffic). Each thread issues one 16-byte load from gate and
+ * one from up, with the streaming cache operator on loads and stores; eight
+ * 256-thread CTAs per SM keep 64 KB in flight per SM, and small CTAs (4 KB per
+ * tensor) keep the ramp and the tail short -- measured on B200 this beats 2, 4
+ * and 8 vectors per thread at every size from 1 to 14449 rows. The
  * reference launches one half2 per thread with no instruction-level
  * parallelism (src/cuda/swiglu.cu:45-63).
  *
@@ -26,13 +28,16 @@
 #include "vvb_launch.h"
 
 #include <atomic>
+#ifdef VVB_TUNING
+#include <cstdlib>
+#endif
 
 namespace vvb {
 
 extern std::atomic<uint64_t> g_launches;
 
 constexpr int kSwigluThreads = 256;
-constexpr int kUnroll = 4;
+constexpr int kSwigluUnroll = 1;
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
     float e, r;
@@ -54,6 +59,7 @@ __device__ __forceinline__ vec16 silu_mul_vec(const vec16& g, const vec16& u) {
 /* gate/up/out rows of `row_vecs` vectors; row r of gate starts at
  * gate + r*gate_stride (vectors), likewise up and out. The flat op is the
  * single-row case. grid.y indexes rows. */
+template <int kUnroll>
 __global__ void __launch_bounds__(kSwigluThreads)
 swiglu_vec_kernel(const vec16* gate, const vec16* up, vec16* out,
                   size_t row_vecs, size_t gate_stride, size_t up_stride, size_t out_stride,
@@ -110,14 +116,31 @@ extern "C" int vvbk_swiglu(const void* gate, const void* up, void* out, size_t n
     if (aligned16(gate) && aligned16(up) && aligned16(out)) {
         const size_t nvec = n / 8;
         const int tail = (int)(n - nvec * 8);
-        const size_t per_cta = (size_t)kSwigluThreads * kUnroll;
+        int unroll = kSwigluUnroll;
+#ifdef VVB_TUNING
+        if (const char* e = getenv("VVB_TUNE_SWIGLU_UNROLL")) unroll = atoi(e);
+#endif
+        const size_t per_cta = (size_t)kSwigluThreads * unroll;
         size_t blocks = (nvec + per_cta - 1) / per_cta;
         if (blocks == 0) blocks = 1;
         if (blocks > 0x7fffffffu) return (int)cudaErrorInvalidValue;
         const __half* tg = (const __half*)gate + nvec * 8;
         const __half* tu = (const __half*)up + nvec * 8;
         __half* to = (__half*)out + nvec * 8;
-        swiglu_vec_kernel<<<dim3((unsigned)blocks, 1), kSwigluThreads, 0, s>>>(
+        const dim3 grid((unsigned)blocks, 1);
+#ifdef VVB_TUNING
+        if (unroll == 1)
+            swiglu_vec_kernel<1><<<grid, kSwigluThreads, 0, s>>>(
+                (const vec16*)gate, (const vec16*)up, (vec16*)out, nvec, 0, 0, 0, tg, tu, to, tail);
+        else if (unroll == 2)
+            swiglu_vec_kernel<2><<<grid, kSwigluThreads, 0, s>>>(
+                (const vec16*)gate, (const vec16*)up, (vec16*)out, nvec, 0, 0, 0, tg, tu, to, tail);
+        else if (unroll == 8)
+            swiglu_vec_kernel<8><<<grid, kSwigluThreads, 0, s>>>(
+                (const vec16*)gate, (const vec16*)up, (vec16*)out, nvec, 0, 0, 0, tg, tu, to, tail);
+        else
+#endif
+        swiglu_vec_kernel<kSwigluUnroll><<<grid, kSwigluThreads, 0, s>>>(
             (const vec16*)gate, (const vec16*)up, (vec16*)out, nvec, 0, 0, 0, tg, tu, to, tail);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return (int)cudaGetLastError();
@@ -141,9 +164,9 @@ extern "C" int vvbk_swiglu_fused(const void* gate_up, void* out, int rows, int i
         __half* o = (__half*)out + (size_t)r0 * (size_t)inter;
         if (inter % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
             const size_t row_vecs = (size_t)inter / 8;
-            const size_t per_cta = (size_t)kSwigluThreads * kUnroll;
+            const size_t per_cta = (size_t)kSwigluThreads * kSwigluUnroll;
             const unsigned bx = (unsigned)((row_vecs + per_cta - 1) / per_cta);
-            swiglu_vec_kernel<<<dim3(bx, (unsigned)nr), kSwigluThreads, 0, s>>>(
+            swiglu_vec_kernel<kSwigluUnroll><<<dim3(bx, (unsigned)nr), kSwigluThreads, 0, s>>>(
                 (const vec16*)gu, (const vec16*)(gu + inter), (vec16*)o,
                 row_vecs, 2 * row_vecs, 2 * row_vecs, row_vecs, nullptr, nullptr, nullptr, 0);
         } else {
