@@ -43,9 +43,12 @@ BYTES_SWIGLU = 3 * INTER * 2              # read gate, up; write out            
 BYTES_CHAIN = BYTES_ADDNORM + BYTES_ROPE + BYTES_SWIGLU   #                     158 720
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per token per launch seen by ncu (dram__bytes_read.sum +
-# dram__bytes_write.sum), from the captures summarised under profiles/;
-# None until a capture exists.
-NCU_DRAM_BYTES_PER_TOKEN = {"swiglu": None, "add_rmsnorm": None, "rope_qk": None}
+# dram__bytes_write.sum at T = 14449, one launch of each kernel; summary in
+# profiles/layer_chain_T14449_launch_list_and_dram.md). Reads equal the
+# algorithmic reads; writes are ~55 MB short of the algorithmic writes because
+# the last lines written are still dirty in L2 when the kernel ends. Scaled by
+# rows for other sizes.
+NCU_DRAM_BYTES_PER_TOKEN = {"swiglu": 110050, "add_rmsnorm": 24590, "rope_qk": 12265}
 CPU_SAMPLE_ROWS = 4096
 
 
