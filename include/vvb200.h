@@ -150,7 +150,11 @@ vv_status_t vvb_residual_add_dev(void* x, const void* y, size_t total, void* str
 
 /** One decoder layer's elementwise chain on one stream, in the engine's
  *  order: add + RMSNorm, RoPE on Q and K, SwiGLU in place on gate
- *  (src/inference/decoder.c:950-977). Three launches. */
+ *  (src/inference/decoder.c:950-977). The three operations touch disjoint
+ *  tensors, so when shapes and alignment allow (hidden_size <= 4096 and a
+ *  multiple of 8, head_dim a multiple of 16, 16-byte aligned pointers) they go
+ *  out as ONE grid whose CTAs are split between them; otherwise as three
+ *  launches. Results are byte-identical either way. */
 typedef struct vvb_layer_chain {
     void* hidden;          /* [rows, hidden_size] in/out */
     const void* delta;     /* [rows, hidden_size] */

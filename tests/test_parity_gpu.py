@@ -217,13 +217,41 @@ def test_config5_chain_slice(vv, orc):
     chain = vv.make_chain(dh, dev(d), dev(w), dn, dq, dk, dg, dev(up), rows, 3584, 28, 4, 128, 18944, first, 1e-6, 1e6)
     n0 = vv.launch_count()
     assert vv.vvb_layer_chain_dev(chain) == 0
-    assert vv.launch_count() - n0 == 3
+    assert vv.launch_count() - n0 == 1      # one grid carries all three operations
     want_h, want_n = orc.add_rmsnorm_f16(h, d, w, 1e-6)
     assert np.array_equal(bits(host(dh)), bits(want_h))
     assert orc.ulp_distance(host(dn), want_n).max() <= NORM_ULP
     assert orc.rope_error_in_ulps(host(dq), orc.rope_f16(q, first, 1e6), q).max() <= ROPE_ULP
     assert orc.rope_error_in_ulps(host(dk), orc.rope_f16(k, first, 1e6), k).max() <= ROPE_ULP
     assert orc.ulp_distance(host(dg), orc.swiglu_f16(gate, up)).max() <= SWIGLU_ULP
+
+
+@pytest.mark.parametrize("rows,H,nq,nkv,hd,inter,expect_launches", [
+    (1, 3584, 28, 4, 128, 18944, 1), (7, 3584, 28, 4, 128, 18944, 1), (1807, 3584, 28, 4, 128, 18944, 1),
+    (48, 256, 2, 1, 128, 512, 1),        # the reference's tiny test model (tests/test_prefill_append.c:30-93)
+    (5, 1536, 12, 2, 128, 8960, 1),      # BitNet-1.5B shape
+    (3, 8192, 8, 8, 64, 1000, 3),        # hidden too wide for the single grid: three launches
+    (3, 250, 2, 1, 10, 33, 3)])          # nothing vectorisable: three launches of scalar kernels
+def test_chain_equals_separate_calls(vv, rows, H, nq, nkv, hd, inter, expect_launches):
+    """vvb_layer_chain_dev (one grid when shapes allow) writes the bytes the
+    three separate entry points write."""
+    rng = np.random.default_rng(rows * 7 + H)
+    h, d = randn16(rng, rows, H), randn16(rng, rows, H)
+    w = (1 + 0.02 * rng.standard_normal(H)).astype(np.float16)
+    q, k = randn16(rng, rows, nq, hd), randn16(rng, rows, nkv, hd)
+    g, u = randn16(rng, rows, inter), randn16(rng, rows, inter)
+    a = [Guarded(x) for x in (h, np.zeros_like(h), q, k, g)]
+    chain = vv.make_chain(a[0].ptr, dev(d), dev(w), a[1].ptr, a[2].ptr, a[3].ptr, a[4].ptr, dev(u), rows, H, nq, nkv,
+                          hd, inter, 77, 1e-6, 1e6)
+    n0 = vv.launch_count()
+    assert vv.vvb_layer_chain_dev(chain) == 0
+    assert vv.launch_count() - n0 == expect_launches
+    b = [Guarded(x) for x in (h, np.zeros_like(h), q, k, g)]
+    assert vv.vvb_add_rmsnorm_dev(b[0].ptr, dev(d), dev(w), b[1].ptr, rows, H, 1e-6) == 0
+    assert vv.vvb_rope_qk_dev(b[2].ptr, b[3].ptr, rows, nq, nkv, hd, 77, None, 1e6) == 0
+    assert vv.vvb_swiglu_dev(b[4].ptr, dev(u), b[4].ptr, rows * inter) == 0
+    for x, y in zip(a, b):
+        assert np.array_equal(bits(x.get()), bits(y.get()))
 
 
 # --------------------------------------------------------------- shapes and edges

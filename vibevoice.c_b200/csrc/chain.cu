@@ -1,0 +1,108 @@
+/*
+ * chain.cu -- one decoder layer's elementwise chain as ONE launch.
+ *
+ * The three operations of the chain (residual add + RMSNorm on the hidden
+ * state, RoPE on Q and K, SwiGLU on gate/up) touch disjoint tensors, so nothing
+ * orders them: a single grid carries the CTAs of all three, block index ranges
+ * selecting the work ([norm | rope | swiglu]). Compared with three launches this
+ * removes two launch ramps and two drains per step -- about 2 us each, which is
+ * a tenth of a step when a 14449-token prompt is sharded over eight GPUs
+ * (1807 rows, ~45 us per GPU) -- because CTAs of the next operation start on an
+ * SM as soon as CTAs of the previous one retire. Every CTA runs exactly the
+ * device body the separate kernels run (row_norm.cuh, rope.cuh, swiglu.cuh), so
+ * results are byte-identical to the three-launch path.
+ *
+ * CTAs are 256 threads: two rows of the norm (two 128-thread groups with a
+ * named barrier each), one RoPE tile, or 4 x 256 SwiGLU vectors.
+ */
+#include "rope.cuh"
+#include "row_norm.cuh"
+#include "swiglu.cuh"
+#include "vvb_launch.h"
+
+#include <atomic>
+
+namespace vvb {
+
+extern std::atomic<uint64_t> g_launches;
+
+constexpr int kChainThreads = 256;
+constexpr int kChainNormGroup = 128;     /* threads per row */
+constexpr int kChainNormVPT = 4;         /* => hidden <= 128 * 4 * 8 = 4096 */
+constexpr int kChainSwigluUnroll = 4;
+
+struct ChainArgs {
+    RowNormArgs norm;
+    RopeArgs rope;
+    const vec16* gate;
+    const vec16* up;
+    vec16* out;
+    size_t swiglu_vecs;
+    unsigned norm_ctas, rope_gx, rope_ctas;
+};
+
+__global__ void __launch_bounds__(kChainThreads, 4)
+layer_chain_kernel(const __grid_constant__ ChainArgs a) {
+    unsigned b = blockIdx.x;
+    const int t = threadIdx.x;
+    if (b < a.norm_ctas) {
+        const int grp = t / kChainNormGroup;
+        row_norm_body<kChainNormVPT, kChainThreads / kChainNormGroup>(
+            a.norm, (int)(b * (kChainThreads / kChainNormGroup)) + grp, t - grp * kChainNormGroup,
+            kChainNormGroup, grp);
+        return;
+    }
+    b -= a.norm_ctas;
+    if (b < a.rope_ctas) {
+        rope_tile_body(a.rope, (int)(b % a.rope_gx), (int)(b / a.rope_gx));
+        return;
+    }
+    b -= a.rope_ctas;
+    swiglu_stream_body<kChainSwigluUnroll, kChainThreads>(a.gate, a.up, a.out, a.swiglu_vecs, b, t);
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace vvb
+
+using namespace vvb;
+
+/* Returns cudaErrorNotSupported (without launching) when the shapes do not fit
+ * the single-launch form; the caller then issues the three launches. */
+extern "C" int vvbk_layer_chain(void* hidden, const void* delta, const void* weight, void* normed,
+                                void* q, void* k, void* gate, const void* up,
+                                int rows, int hidden_size, int n_q_heads, int n_kv_heads, int head_dim,
+                                int inter, int position_offset, const float* inv_freq, float eps,
+                                void* stream) {
+    const int nvec = hidden_size / 8;
+    const size_t n = (size_t)rows * (size_t)inter;
+    const bool fits = rows > 0 && hidden_size > 0 && hidden_size % 8 == 0 &&
+                      nvec <= kChainNormGroup * kChainNormVPT && delta != nullptr &&
+                      head_dim >= 16 && head_dim % 16 == 0 && head_dim / 2 <= VVB_ROPE_MAX_HALF &&
+                      n_q_heads + n_kv_heads > 0 && n > 0 && n % 8 == 0 &&
+                      aligned16(hidden) && aligned16(delta) && aligned16(weight) && aligned16(normed) &&
+                      aligned16(q) && aligned16(k) && aligned16(gate) && aligned16(up);
+    if (!fits) return (int)cudaErrorNotSupported;
+
+    ChainArgs a;
+    a.norm = RowNormArgs{(const vec16*)hidden, (const vec16*)delta, nullptr, (vec16*)hidden,
+                         (const vec16*)weight, (vec16*)normed, rows, nvec, hidden_size, 0, eps};
+    unsigned gx, gy;
+    rope_plan(a.rope, q, k, rows, n_q_heads, n_kv_heads, head_dim, position_offset, nullptr, inv_freq,
+              kRopeMaxRowsPerThread, &gx, &gy);
+    a.gate = (const vec16*)gate;
+    a.up = (const vec16*)up;
+    a.out = (vec16*)gate;
+    a.swiglu_vecs = n / 8;
+    const unsigned rows_per_cta = kChainThreads / kChainNormGroup;
+    a.norm_ctas = ((unsigned)rows + rows_per_cta - 1) / rows_per_cta;
+    a.rope_gx = gx;
+    a.rope_ctas = gx * gy;
+    const size_t per_cta = (size_t)kChainThreads * kChainSwigluUnroll;
+    const size_t swiglu_ctas = (a.swiglu_vecs + per_cta - 1) / per_cta;
+    const size_t total = (size_t)a.norm_ctas + a.rope_ctas + swiglu_ctas;
+    if (total > 0x7fffffffu) return (int)cudaErrorNotSupported;
+    layer_chain_kernel<<<(unsigned)total, kChainThreads, 0, (cudaStream_t)stream>>>(a);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return (int)cudaGetLastError();
+}

@@ -29,7 +29,7 @@
  * any, and it writes exactly the indices it read, so delta == normed and
  * input == output are safe.
  */
-#include "vvb_device.cuh"
+#include "row_norm.cuh"
 #include "vvb_launch.h"
 
 #include <atomic>
@@ -41,114 +41,11 @@ namespace vvb {
 
 extern std::atomic<uint64_t> g_launches;
 
-struct RowNormArgs {
-    const vec16* src;     /* rows or table */
-    const vec16* delta;   /* may be null */
-    const int32_t* ids;   /* may be null */
-    vec16* row_out;       /* may be null */
-    const vec16* weight;
-    vec16* normed;        /* never null in the norm kernel */
-    int rows;
-    int nvec;             /* hidden / 8 */
-    int hidden;
-    int vocab;
-    float eps;
-};
-
-__device__ __forceinline__ float inv_rms(double ss, int hidden, float eps) {
-    const float mean = (float)(ss / (double)hidden);
-    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
-}
-
-__device__ __forceinline__ vec16 scale_row_vec(const vec16& h, const vec16& w, float inv) {
-    float f[8], g[8];
-    unpack8(h, f);
-    unpack8(w, g);
-#pragma unroll
-    for (int e = 0; e < 8; e++) f[e] = __fmul_rn(__fmul_rn(f[e], inv), g[e]);
-    return pack8(f);
-}
-
 /* ----------------------------------------------------------------- CTA/row */
 template <int VPT>
 __global__ void __launch_bounds__(1024)
 row_norm_cta_kernel(const RowNormArgs a) {
-    __shared__ double red[32];
-    const int t = threadIdx.x, G = blockDim.x;
-    const int row = blockIdx.x;
-    const size_t roff = (size_t)row * (size_t)a.nvec;
-
-    size_t srow = (size_t)row;
-    if (a.ids != nullptr) {
-        int id = a.ids[row];
-        if (a.vocab > 0) id = min(max(id, 0), a.vocab - 1);
-        srow = (size_t)id;
-    }
-    const vec16* sp = a.src + srow * (size_t)a.nvec;
-    const bool has_delta = (a.delta != nullptr);
-
-    /* Every load of the row, the addend and gamma goes out before any is used. */
-    vec16 hv[VPT], dv[VPT], wv[VPT];
-#pragma unroll
-    for (int j = 0; j < VPT; j++) {
-        const int v = t + j * G;
-        hv[j] = (v < a.nvec) ? ld_stream(sp + v) : make_uint4(0, 0, 0, 0);
-    }
-    if (has_delta) {
-        const vec16* dp = a.delta + roff;
-#pragma unroll
-        for (int j = 0; j < VPT; j++) {
-            const int v = t + j * G;
-            dv[j] = (v < a.nvec) ? ld_stream(dp + v) : make_uint4(0, 0, 0, 0);
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < VPT; j++) {
-        const int v = t + j * G;
-        wv[j] = (v < a.nvec) ? __ldg(a.weight + v) : make_uint4(0, 0, 0, 0);
-    }
-
-    double ss = 0.0;
-#pragma unroll
-    for (int j = 0; j < VPT; j++) {
-        float f[8];
-        unpack8(hv[j], f);
-        if (has_delta) {
-            float d[8];
-            unpack8(dv[j], d);
-#pragma unroll
-            for (int e = 0; e < 8; e++) f[e] = __fadd_rn(f[e], d[e]);
-            hv[j] = pack8(f);       /* round to FP16: this is the new hidden state */
-            unpack8(hv[j], f);      /* and the norm sees the rounded values */
-        }
-#pragma unroll
-        for (int e = 0; e < 8; e++) ss = fma((double)f[e], (double)f[e], ss);
-    }
-    if (a.row_out != nullptr) {
-        vec16* rp = a.row_out + roff;
-#pragma unroll
-        for (int j = 0; j < VPT; j++) {
-            const int v = t + j * G;
-            if (v < a.nvec) st_stream(rp + v, hv[j]);
-        }
-    }
-
-    ss = warp_sum(ss);
-    if ((t & 31) == 0) red[t >> 5] = ss;
-    __syncthreads();
-    /* every thread adds the warp sums in the same order: one barrier, and all
-     * threads hold the same total */
-    ss = 0.0;
-    const int nwarps = G >> 5;
-    for (int w = 0; w < nwarps; w++) ss += red[w];
-    const float inv = inv_rms(ss, a.hidden, a.eps);
-
-    vec16* np_ = a.normed + roff;
-#pragma unroll
-    for (int j = 0; j < VPT; j++) {
-        const int v = t + j * G;
-        if (v < a.nvec) st_stream(np_ + v, scale_row_vec(hv[j], wv[j], inv));
-    }
+    row_norm_body<VPT, 1>(a, blockIdx.x, threadIdx.x, blockDim.x, 0);
 }
 
 /* ----------------------------------------------------------------- generic */

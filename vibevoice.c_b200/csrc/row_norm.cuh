@@ -1,0 +1,127 @@
+/*
+ * row_norm.cuh -- arguments and the per-row device body of the RMSNorm family
+ * (RMSNorm, residual add + RMSNorm, gather + RMSNorm), shared by the row
+ * kernel (row_norm.cu) and the single-launch layer chain (chain.cu).
+ * The arithmetic is documented at the top of row_norm.cu.
+ */
+#pragma once
+#include "vvb_device.cuh"
+
+namespace vvb {
+
+struct RowNormArgs {
+    const vec16* src;     /* rows or table */
+    const vec16* delta;   /* may be null */
+    const int32_t* ids;   /* may be null */
+    vec16* row_out;       /* may be null */
+    const vec16* weight;
+    vec16* normed;        /* never null in the norm kernel */
+    int rows;
+    int nvec;             /* hidden / 8 */
+    int hidden;
+    int vocab;
+    float eps;
+};
+
+__device__ __forceinline__ float inv_rms(double ss, int hidden, float eps) {
+    const float mean = (float)(ss / (double)hidden);
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+}
+
+__device__ __forceinline__ vec16 scale_row_vec(const vec16& h, const vec16& w, float inv) {
+    float f[8], g[8];
+    unpack8(h, f);
+    unpack8(w, g);
+#pragma unroll
+    for (int e = 0; e < 8; e++) f[e] = __fmul_rn(__fmul_rn(f[e], inv), g[e]);
+    return pack8(f);
+}
+
+/* ------------------------------------------------------------ one row, one group
+ * GROUPS groups of `G` threads share a CTA, one row each (GROUPS == 1: the
+ * group is the whole CTA). t = thread index within the group. */
+template <int VPT, int GROUPS>
+__device__ __forceinline__ void row_norm_body(const RowNormArgs& a, int row, int t, int G, int grp) {
+    __shared__ double red[GROUPS][32];
+    const bool have = row < a.rows;
+    const size_t roff = (size_t)(have ? row : 0) * (size_t)a.nvec;
+    const int nvec = have ? a.nvec : 0;          /* a group without a row loads and stores nothing */
+
+    size_t srow = (size_t)(have ? row : 0);
+    if (have && a.ids != nullptr) {
+        int id = a.ids[row];
+        if (a.vocab > 0) id = min(max(id, 0), a.vocab - 1);
+        srow = (size_t)id;
+    }
+    const vec16* sp = a.src + srow * (size_t)a.nvec;
+    const bool has_delta = (a.delta != nullptr);
+
+    /* Every load of the row, the addend and gamma goes out before any is used. */
+    vec16 hv[VPT], dv[VPT], wv[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        const int v = t + j * G;
+        hv[j] = (v < nvec) ? ld_stream(sp + v) : make_uint4(0, 0, 0, 0);
+    }
+    if (has_delta) {
+        const vec16* dp = a.delta + roff;
+#pragma unroll
+        for (int j = 0; j < VPT; j++) {
+            const int v = t + j * G;
+            dv[j] = (v < nvec) ? ld_stream(dp + v) : make_uint4(0, 0, 0, 0);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        const int v = t + j * G;
+        wv[j] = (v < nvec) ? __ldg(a.weight + v) : make_uint4(0, 0, 0, 0);
+    }
+
+    double ss = 0.0;
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        float f[8];
+        unpack8(hv[j], f);
+        if (has_delta) {
+            float d[8];
+            unpack8(dv[j], d);
+#pragma unroll
+            for (int e = 0; e < 8; e++) f[e] = __fadd_rn(f[e], d[e]);
+            hv[j] = pack8(f);       /* round to FP16: this is the new hidden state */
+            unpack8(hv[j], f);      /* and the norm sees the rounded values */
+        }
+#pragma unroll
+        for (int e = 0; e < 8; e++) ss = fma((double)f[e], (double)f[e], ss);
+    }
+    if (a.row_out != nullptr) {
+        vec16* rp = a.row_out + roff;
+#pragma unroll
+        for (int j = 0; j < VPT; j++) {
+            const int v = t + j * G;
+            if (v < nvec) st_stream(rp + v, hv[j]);
+        }
+    }
+
+    ss = warp_sum(ss);
+    if ((t & 31) == 0) red[grp][t >> 5] = ss;
+    if (GROUPS == 1) {
+        __syncthreads();
+    } else {
+        asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "r"(G) : "memory");
+    }
+    /* every thread adds the warp sums in the same order: one barrier, and all
+     * threads hold the same total */
+    ss = 0.0;
+    const int nwarps = G >> 5;
+    for (int w = 0; w < nwarps; w++) ss += red[grp][w];
+    const float inv = inv_rms(ss, a.hidden, a.eps);
+
+    vec16* np_ = a.normed + roff;
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        const int v = t + j * G;
+        if (v < nvec) st_stream(np_ + v, scale_row_vec(hv[j], wv[j], inv));
+    }
+}
+
+}  // namespace vvb

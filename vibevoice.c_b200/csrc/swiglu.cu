@@ -24,7 +24,7 @@
  * out == gate (the engine's call, src/inference/decoder.c:977) and out == up
  * are safe: a thread writes only indices it has already read.
  */
-#include "vvb_device.cuh"
+#include "swiglu.cuh"
 #include "vvb_launch.h"
 
 #include <atomic>
@@ -39,23 +39,6 @@ extern std::atomic<uint64_t> g_launches;
 constexpr int kSwigluThreads = 256;
 constexpr int kSwigluUnroll = 1;
 
-__device__ __forceinline__ float silu_mul(float g, float u) {
-    float e, r;
-    const float p = __fmul_rn(g, -1.4426950408889634f);               /* -g * log2(e) */
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(p));            /* exp(-g) */
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(__fadd_rn(1.0f, e)));
-    return __fmul_rn(__fmul_rn(g, r), u);
-}
-
-__device__ __forceinline__ vec16 silu_mul_vec(const vec16& g, const vec16& u) {
-    float a[8], b[8];
-    unpack8(g, a);
-    unpack8(u, b);
-#pragma unroll
-    for (int e = 0; e < 8; e++) a[e] = silu_mul(a[e], b[e]);
-    return pack8(a);
-}
-
 /* gate/up/out rows of `row_vecs` vectors; row r of gate starts at
  * gate + r*gate_stride (vectors), likewise up and out. The flat op is the
  * single-row case. grid.y indexes rows. */
@@ -68,21 +51,7 @@ swiglu_vec_kernel(const vec16* gate, const vec16* up, vec16* out,
     const vec16* g = gate + r * gate_stride;
     const vec16* u = up + r * up_stride;
     vec16* o = out + r * out_stride;
-    const size_t base = (size_t)blockIdx.x * (kSwigluThreads * kUnroll) + threadIdx.x;
-    vec16 gv[kUnroll], uv[kUnroll];
-#pragma unroll
-    for (int j = 0; j < kUnroll; j++) {
-        const size_t v = base + (size_t)j * kSwigluThreads;
-        if (v < row_vecs) {
-            gv[j] = ld_stream(g + v);
-            uv[j] = ld_stream(u + v);
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < kUnroll; j++) {
-        const size_t v = base + (size_t)j * kSwigluThreads;
-        if (v < row_vecs) st_stream(o + v, silu_mul_vec(gv[j], uv[j]));
-    }
+    swiglu_stream_body<kUnroll, kSwigluThreads>(g, u, o, row_vecs, blockIdx.x, threadIdx.x);
     /* up to 7 trailing elements of a flat call whose n is not a multiple of 8 */
     if (tail > 0 && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < tail) {
         const int i = threadIdx.x;

@@ -38,6 +38,14 @@ int vvbk_rope(void* q, void* k, int rows, int n_q_heads, int n_kv_heads, int hea
 int vvbk_swiglu(const void* gate, const void* up, void* out, size_t n, void* stream);
 int vvbk_swiglu_fused(const void* gate_up, void* out, int rows, int inter, void* stream);
 
+/* The whole layer chain in one launch (csrc/chain.cu). Returns
+ * cudaErrorNotSupported (801) without launching when the shapes or alignments
+ * do not fit that form. */
+int vvbk_layer_chain(void* hidden, const void* delta, const void* weight, void* normed,
+                     void* q, void* k, void* gate, const void* up,
+                     int rows, int hidden_size, int n_q_heads, int n_kv_heads, int head_dim,
+                     int inter, int position_offset, const float* inv_freq, float eps, void* stream);
+
 /* Flat elementwise ops (csrc/elementwise.cu). */
 int vvbk_residual_add(void* x, const void* y, size_t n, void* stream);
 int vvbk_bias_add(void* out, const void* bias, int M, int N, void* stream);

@@ -155,7 +155,22 @@ vv_status_t vvb_embedding_rmsnorm_dev(const void* table, const int32_t* ids,
 
 vv_status_t vvb_layer_chain_dev(const vvb_layer_chain_t* c, void* stream) {
     if (!c) return VV_ERR_NULL_PTR;
-    if (c->rows < 0 || c->hidden_size < 0 || c->inter < 0) return VV_ERR_INVALID_ARG;
+    if (c->rows < 0 || c->hidden_size < 0 || c->inter < 0 || c->n_q_heads < 0 ||
+        c->n_kv_heads < 0 || c->head_dim < 0)
+        return VV_ERR_INVALID_ARG;
+    /* The three operations touch disjoint tensors: when the shapes allow it
+     * they go out as one grid (csrc/chain.cu), else as three launches. */
+    if (c->rows > 0 && c->hidden && c->delta && c->norm_w && c->normed && c->q && c->k &&
+        c->gate && c->up && c->head_dim >= 2 && c->head_dim / 2 <= VVB_ROPE_MAX_HALF) {
+        float inv_freq[VVB_ROPE_MAX_HALF];
+        fill_inv_freq(inv_freq, c->head_dim, c->theta);
+        const int err = vvbk_layer_chain(c->hidden, c->delta, c->norm_w, c->normed, c->q, c->k,
+                                         c->gate, c->up, c->rows, c->hidden_size, c->n_q_heads,
+                                         c->n_kv_heads, c->head_dim, c->inter, c->position_offset,
+                                         inv_freq, c->eps, stream);
+        if (err != 801 /* cudaErrorNotSupported: shapes do not fit the single launch */)
+            return from_cuda(err);
+    }
     vv_status_t st = vvb_add_rmsnorm_dev(c->hidden, c->delta, c->norm_w, c->normed,
                                          c->rows, c->hidden_size, c->eps, stream);
     if (st != VV_OK) return st;
