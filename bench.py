@@ -48,7 +48,7 @@ FALLBACK_HBM_GBS = 6650.0
 # algorithmic reads; writes are ~55 MB short of the algorithmic writes because
 # the last lines written are still dirty in L2 when the kernel ends. Scaled by
 # rows for other sizes.
-NCU_DRAM_BYTES_PER_TOKEN = {"layer_chain": None, "swiglu": 110050, "add_rmsnorm": 24590, "rope_qk": 12265}
+NCU_DRAM_BYTES_PER_TOKEN = {"layer_chain": 155230, "swiglu": 110050, "add_rmsnorm": 24590, "rope_qk": 12265}
 CPU_SAMPLE_ROWS = 4096
 
 
