@@ -110,6 +110,44 @@ vv_status_t vv_bias_add_dev(void* output, const void* bias, int M, int N, void* 
 vv_status_t vv_fp32_to_fp16_dev(const void* in_fp32, void* out_fp16, int n, void* stream);
 vv_status_t vv_fp16_to_fp32_dev(const void* in_fp16, void* out_fp32, int n, void* stream);
 
+/* ---- per-token int8 activations (the W8A8 / W4A8 layers' inputs) -------- *
+ * sx[m] = max|v[m,:]| / 127, xq = clamp(round-half-even(v * 127 / max|v|),
+ * -127, 127), where v is the FP16 value the unfused op would have written;
+ * xsum (optional, may be NULL) = sum of xq over each run of 32 columns,
+ * [M][K/32]. `layout` orders the bytes inside each run of 32 columns
+ * (include/vibevoice/q8.h:19-60). K must be a multiple of 32 and at most
+ * VV_ACT_QUANT_MAX_K, M > 0 (the reference's checks and codes:
+ * src/cuda/act_quant.cu:222-233). A row is bit-identical to "op, then
+ * vv_act_quant_dev" and to the reference's CPU quantizer on the same values. */
+#ifndef VV_Q8_H
+typedef enum vv_q8_layout {
+    VV_Q8_NATURAL = 0,   /* column order */
+    VV_Q8_NIBBLE = 1,    /* the 16 even columns, then the 16 odd ones */
+    VV_Q8_W4_GEMV = 2,   /* byte order of the W4A16 GPU layout, for the W4A8 GEMV */
+    VV_Q8_W4_MMA = 3,    /* the same, arranged for mma.m16n8k32 */
+    VV_Q8_LAYOUT_COUNT
+} vv_q8_layout_t;
+#endif
+#ifndef VV_ACT_QUANT_MAX_K
+#define VV_ACT_QUANT_MAX_K 22528   /* include/vibevoice/device.h:313 */
+#define VV_ACT_QUANT_MIN_K 256     /* include/vibevoice/device.h:315: narrowest row of vv_rmsnorm_q8_dev */
+#endif
+
+/** FP16 [M,K] -> int8 [M,K] + FP32 scale [M] (+ xsum). Replaces
+ *  include/vibevoice/device.h:317-320 (src/cuda/act_quant.cu:235). */
+vv_status_t vv_act_quant_dev(const void* x, int M, int K, int layout,
+                             int8_t* xq, float* sx, int32_t* xsum, void* stream);
+
+/** RMSNorm fused with the quantizer. Replaces include/vibevoice/device.h:322-326
+ *  (src/cuda/act_quant.cu:247). The FP16 value quantized is vv_rmsnorm_dev's. */
+vv_status_t vv_rmsnorm_q8_dev(const void* x, const void* weight, int M, int K, float eps,
+                              int layout, int8_t* xq, float* sx, int32_t* xsum, void* stream);
+
+/** SwiGLU fused with the quantizer. Replaces include/vibevoice/device.h:328-331
+ *  (src/cuda/act_quant.cu:264). The FP16 value quantized is vv_swiglu_dev's. */
+vv_status_t vv_swiglu_q8_dev(const void* gate, const void* up, int M, int K, int layout,
+                             int8_t* xq, float* sx, int32_t* xsum, void* stream);
+
 /* ====================================================================== *
  *  Group 2 -- additive entry points (no counterpart symbol in the          *
  *  reference; each states the reference call sequence it equals)           *
@@ -123,6 +161,13 @@ vv_status_t vv_fp16_to_fp32_dev(const void* in_fp16, void* out_fp32, int n, void
 vv_status_t vvb_add_rmsnorm_dev(void* hidden_inout, const void* delta,
                                 const void* weight, void* normed_out,
                                 int rows, int hidden_size, float eps, void* stream);
+
+/** hidden = f16(hidden + delta), then RMSNorm + int8 quantization of the
+ *  updated row in one kernel: vv_residual_add_dev + vv_rmsnorm_q8_dev
+ *  (src/inference/decoder.c:950 then :920). delta == NULL skips the add. */
+vv_status_t vvb_add_rmsnorm_q8_dev(void* hidden_inout, const void* delta, const void* weight,
+                                   int M, int K, float eps, int layout,
+                                   int8_t* xq, float* sx, int32_t* xsum, void* stream);
 
 /** vv_rope_dev on Q[rows, n_q_heads, head_dim] and K[rows, n_kv_heads,
  *  head_dim] in one launch, cos/sin computed once per row for both

@@ -28,6 +28,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(_HERE, "liboracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "libvvref_cpu.so")
+REF_INT8_SO = os.path.join(_HERE, "_ref", "libvvref_int8.so")
 
 _f32p = C.POINTER(C.c_float)
 _u16p = C.POINTER(C.c_uint16)
@@ -119,6 +120,39 @@ class _Restated:
     def threads(self):
         return int(self.lib.orc_threads())
 
+    def quant_act_q8(self, x_f32, layout, want_xsum=True):
+        """Per-token int8 quantizer on FP32 rows [M, K]: (xq int8 [M,K],
+        sx float32 [M], xsum int32 [M, K/32] or None)."""
+        L = self.lib
+        L.orc_quant_act_q8.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, C.c_void_p, _f32p, C.c_void_p]
+        M, K = x_f32.shape
+        xq = np.empty((M, K), np.int8)
+        sx = np.empty(M, np.float32)
+        xsum = np.empty((M, K // 32), np.int32) if want_xsum else None
+        st = L.orc_quant_act_q8(_ptr(np.ascontiguousarray(x_f32), _f32p), M, K, int(layout), xq.ctypes.data,
+                                _ptr(sx, _f32p), xsum.ctypes.data if want_xsum else None)
+        assert st == 0, st
+        return xq, sx, xsum
+
+
+class _ReferenceInt8:
+    """The reference's own quantizer, vv_quant_act_q8_cpu
+    (src/cpu/cpu_int8.c:181-194), compiled unmodified."""
+
+    def __init__(self):
+        self.lib = C.CDLL(REF_INT8_SO)
+        self.lib.vv_quant_act_q8_cpu.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, C.c_void_p, _f32p, C.c_void_p]
+
+    def quant_act_q8(self, x_f32, layout, want_xsum=True):
+        M, K = x_f32.shape
+        xq = np.empty((M, K), np.int8)
+        sx = np.empty(M, np.float32)
+        xsum = np.empty((M, K // 32), np.int32) if want_xsum else None
+        st = self.lib.vv_quant_act_q8_cpu(_ptr(np.ascontiguousarray(x_f32), _f32p), M, K, int(layout),
+                                          xq.ctypes.data, _ptr(sx, _f32p), xsum.ctypes.data if want_xsum else None)
+        assert st == 0, st
+        return xq, sx, xsum
+
 
 class _Reference:
     """ctypes face of the reference's compiled CPU kernels
@@ -196,6 +230,14 @@ def restated() -> _Restated:
 
 def have_reference() -> bool:
     return os.path.exists(REF_SO)
+
+
+def have_reference_int8() -> bool:
+    return os.path.exists(REF_INT8_SO)
+
+
+def reference_int8() -> _ReferenceInt8:
+    return _ReferenceInt8()
 
 
 def reference() -> _Reference:

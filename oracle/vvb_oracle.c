@@ -277,3 +277,51 @@ int orc_threads(void) {
     return 1;
 #endif
 }
+
+/* ---- per-token int8 activation quantizer (src/cpu/cpu_int8.c:158-190) ----
+ * amax = max|x| over the row; inv = 127/amax (0 for an all-zero row);
+ * sx = amax/127; q = clamp(rintf(x*inv), -127, 127) stored at
+ * orc_q8_pos(layout, j) inside each run of 32 columns; xsum = sum of q per run. */
+
+/* Where column j (0..31) of a run is stored (include/vibevoice/q8.h:64-73). */
+int orc_q8_pos(int layout, int j) {
+    const int odd = j & 1, word = (j >> 1) & 3, slot = (j >> 3) + 4 * odd;
+    if (layout == 1) return odd ? 16 + (j >> 1) : (j >> 1);               /* NIBBLE  */
+    if (layout == 2) return 8 * word + 4 * (slot & 1) + (slot >> 1);      /* W4_GEMV */
+    if (layout == 3) return 16 * odd + 4 * word + (slot & 3);             /* W4_MMA  */
+    return j;                                                             /* NATURAL */
+}
+
+int orc_quant_act_q8(const float* x, int M, int K, int layout,
+                     int8_t* xq, float* sx, int32_t* xsum) {
+    if (!x || !xq || !sx) return ORC_ERR_NULL_PTR;
+    if (M <= 0 || K <= 0 || (K % 32) != 0 || layout < 0 || layout > 3) return ORC_ERR_INVALID_ARG;
+    int pos[32];
+    for (int j = 0; j < 32; j++) pos[j] = orc_q8_pos(layout, j);
+    int m;
+#pragma omp parallel for schedule(static)
+    for (m = 0; m < M; m++) {
+        const float* row = x + (size_t)m * (size_t)K;
+        int8_t* q = xq + (size_t)m * (size_t)K;
+        float amax = 0.0f;
+        for (int k = 0; k < K; k++) {
+            const float a = fabsf(row[k]);
+            if (a > amax) amax = a;
+        }
+        const float inv = (amax > 0.0f) ? 127.0f / amax : 0.0f;
+        sx[m] = amax / 127.0f;
+        for (int run = 0; run < K / 32; run++) {
+            int s = 0;
+            for (int j = 0; j < 32; j++) {
+                float v = rintf(row[run * 32 + j] * inv);
+                if (v > 127.0f) v = 127.0f;
+                if (v < -127.0f) v = -127.0f;
+                const int qi = (int)v;
+                s += qi;
+                q[run * 32 + pos[j]] = (int8_t)qi;
+            }
+            if (xsum) xsum[(size_t)m * (size_t)(K / 32) + run] = s;
+        }
+    }
+    return ORC_OK;
+}

@@ -1,0 +1,189 @@
+/*
+ * act_quant.cu -- per-token int8 activation quantization fused into the op
+ * that produces the activation: plain (attention output -> o_proj), RMSNorm
+ * (-> q/k/v and gate/up) and SwiGLU (-> down). sm_100a, HBM-bound.
+ *
+ * Contract (include/vibevoice/device.h:297-333, src/cuda/act_quant.cu:11-22):
+ *   amax = max |v| over the row of FP16 values v the unfused op would write
+ *   sx   = amax / 127                     inv = 127 / amax (0 for a zero row)
+ *   q    = clamp(round-half-even(v * inv), -127, 127)
+ * stored inside each run of 32 columns in the order the reading GEMM wants
+ * (include/vibevoice/q8.h:19-73), plus the optional sum of q per run. Every
+ * step is an explicitly rounded operation, so a row is bit-identical to "op,
+ * then vv_act_quant_dev" and to the reference's CPU quantizer
+ * (src/cpu/cpu_int8.c:158-190) on the same FP16 values.
+ *
+ * One CTA per row, the row in REGISTERS (a quarter of its 16-byte vectors per
+ * thread, as in the row-norm kernel) instead of the reference's shared-memory
+ * copy: the FP16 row is produced, its absolute maximum reduced with warp
+ * shuffles and one shared-memory step, and each thread quantizes the vectors
+ * it holds. The RMSNorm variant is the same device code as vv_rmsnorm_dev
+ * (row_norm.cuh), the SwiGLU variant the same as vv_swiglu_dev (swiglu.cuh),
+ * so "fused == unfused then quantized" holds by construction.
+ */
+#include "row_norm.cuh"
+#include "swiglu.cuh"
+#include "vvb_launch.h"
+
+#include <atomic>
+
+namespace vvb {
+
+extern std::atomic<uint64_t> g_launches;
+
+enum { Q_PLAIN = 0, Q_RMSNORM = 1, Q_SWIGLU = 2 };
+
+struct ActQuantArgs {
+    RowNormArgs norm;        /* Q_RMSNORM: src/delta/row_out/weight/eps; normed unused */
+    const vec16* a;          /* Q_PLAIN: x;  Q_SWIGLU: gate */
+    const vec16* b;          /* Q_SWIGLU: up */
+    int8_t* xq;
+    float* sx;
+    int32_t* xsum;           /* may be null */
+    int rows, nvec, layout;
+};
+
+/* Column j (0..31) of a run -> byte position (include/vibevoice/q8.h:64-73). */
+__device__ __forceinline__ int q8_pos(int layout, int j) {
+    const int odd = j & 1, word = (j >> 1) & 3, slot = (j >> 3) + 4 * odd;
+    if (layout == 1) return odd ? 16 + (j >> 1) : (j >> 1);
+    if (layout == 2) return 8 * word + 4 * (slot & 1) + (slot >> 1);
+    if (layout == 3) return 16 * odd + 4 * word + (slot & 3);
+    return j;
+}
+
+template <int VPT, int MODE>
+__global__ void __launch_bounds__(1024)
+act_quant_kernel(const ActQuantArgs a) {
+    __shared__ float red_max[32];
+    const int t = threadIdx.x, G = blockDim.x;
+    const int row = blockIdx.x;
+    const size_t roff = (size_t)row * (size_t)a.nvec;
+
+    /* 1. the FP16 row the unfused op would write, in registers */
+    vec16 yv[VPT];
+    if (MODE == Q_RMSNORM) {
+        row_norm_produce<VPT, 1>(a.norm, row, t, G, 0, yv);
+    } else {
+        vec16 bv[VPT];
+#pragma unroll
+        for (int j = 0; j < VPT; j++) {
+            const int v = t + j * G;
+            yv[j] = (v < a.nvec) ? ld_stream(a.a + roff + v) : make_uint4(0, 0, 0, 0);
+            if (MODE == Q_SWIGLU) bv[j] = (v < a.nvec) ? ld_stream(a.b + roff + v) : make_uint4(0, 0, 0, 0);
+        }
+        if (MODE == Q_SWIGLU) {
+#pragma unroll
+            for (int j = 0; j < VPT; j++) yv[j] = silu_mul_vec(yv[j], bv[j]);
+        }
+    }
+
+    /* 2. absolute maximum of the row */
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        float f[8];
+        unpack8(yv[j], f);
+#pragma unroll
+        for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(f[e]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((t & 31) == 0) red_max[t >> 5] = amax;
+    __syncthreads();
+    amax = 0.0f;
+    for (int w = 0; w < (G >> 5); w++) amax = fmaxf(amax, red_max[w]);
+
+    const float inv = (amax > 0.0f) ? __fdiv_rn(127.0f, amax) : 0.0f;
+    if (t == 0) a.sx[row] = __fdiv_rn(amax, 127.0f);
+
+    /* 3. quantize the vectors this thread holds. Vector v covers columns
+     * 8v..8v+7: chunk i = v & 3 of run v >> 2. Four consecutive threads hold
+     * the four chunks of a run (G is a multiple of 32), which is what the
+     * per-run sum needs. */
+    int8_t* xq = a.xq + (size_t)row * (size_t)a.nvec * 8u;
+    int32_t* xsum = a.xsum ? a.xsum + (size_t)row * (size_t)(a.nvec >> 2) : nullptr;
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        const int v = t + j * G;
+        const bool ok = v < a.nvec;
+        float f[8];
+        unpack8(yv[j], f);
+        int s = 0;
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            int q = __float2int_rn(__fmul_rn(f[e], inv));
+            q = max(-127, min(127, q));
+            s += q;
+            const uint32_t byte = (uint32_t)(q & 0xFF);
+            if (e < 4) lo |= byte << (8 * e);
+            else hi |= byte << (8 * (e - 4));
+        }
+        if (ok) {
+            int8_t* run = xq + ((size_t)(v >> 2) << 5);
+            const int i = v & 3;
+            if (a.layout == 0) {
+                *reinterpret_cast<uint2*>(run + (i << 3)) = make_uint2(lo, hi);
+            } else if (a.layout == 1) {
+                /* evens of the chunk at 4i.., odds at 16 + 4i.. */
+                *reinterpret_cast<uint32_t*>(run + (i << 2)) = __byte_perm(lo, hi, 0x6420);
+                *reinterpret_cast<uint32_t*>(run + 16 + (i << 2)) = __byte_perm(lo, hi, 0x7531);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const uint32_t w = e < 4 ? lo : hi;
+                    run[q8_pos(a.layout, (i << 3) + e)] = (int8_t)(w >> (8 * (e & 3)));
+                }
+            }
+        }
+        if (xsum != nullptr) {
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            if (ok && (t & 3) == 0) xsum[v >> 2] = s;
+        }
+    }
+}
+
+template <int MODE>
+static cudaError_t launch_q(const ActQuantArgs& a, cudaStream_t s) {
+    int threads = (((a.nvec + 3) / 4) + 31) / 32 * 32;
+    if (threads > 1024) threads = 1024;
+    int vpt = (a.nvec + threads - 1) / threads;
+    if (vpt == 3) vpt = 4;
+    switch (vpt) {
+        case 1: act_quant_kernel<1, MODE><<<a.rows, threads, 0, s>>>(a); break;
+        case 2: act_quant_kernel<2, MODE><<<a.rows, threads, 0, s>>>(a); break;
+        case 4: act_quant_kernel<4, MODE><<<a.rows, threads, 0, s>>>(a); break;
+        default: return cudaErrorInvalidValue;
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError();
+}
+
+}  // namespace vvb
+
+using namespace vvb;
+
+/* mode 0: x -> q8; mode 1: rmsnorm(a [+ b as delta, updated row to row_out]) -> q8;
+ * mode 2: swiglu(a = gate, b = up) -> q8. K is a multiple of 32 and all
+ * pointers are 16-byte aligned (checked by the caller). */
+extern "C" int vvbk_act_quant(int mode, const void* a, const void* b, const void* weight, void* row_out,
+                              int M, int K, float eps, int layout,
+                              int8_t* xq, float* sx, int32_t* xsum, void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    ActQuantArgs q;
+    q.a = (const vec16*)a;
+    q.b = (const vec16*)b;
+    q.xq = xq;
+    q.sx = sx;
+    q.xsum = xsum;
+    q.rows = M;
+    q.nvec = K / 8;
+    q.layout = layout;
+    q.norm = RowNormArgs{(const vec16*)a, (const vec16*)b, nullptr, (vec16*)row_out, (const vec16*)weight,
+                         nullptr, M, K / 8, K, 0, eps};
+    if (mode == Q_RMSNORM) return (int)launch_q<Q_RMSNORM>(q, s);
+    if (mode == Q_SWIGLU) return (int)launch_q<Q_SWIGLU>(q, s);
+    return (int)launch_q<Q_PLAIN>(q, s);
+}

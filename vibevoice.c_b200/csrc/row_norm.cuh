@@ -40,8 +40,12 @@ __device__ __forceinline__ vec16 scale_row_vec(const vec16& h, const vec16& w, f
 /* ------------------------------------------------------------ one row, one group
  * GROUPS groups of `G` threads share a CTA, one row each (GROUPS == 1: the
  * group is the whole CTA). t = thread index within the group. */
+/* Phase 1: loads the row (and addend, gamma), stores the updated row if asked,
+ * reduces the sum of squares and leaves the NORMALISED row, rounded to FP16, in
+ * yv[] (vector v = t + j*G in yv[j]; zeros beyond the row). */
 template <int VPT, int GROUPS>
-__device__ __forceinline__ void row_norm_body(const RowNormArgs& a, int row, int t, int G, int grp) {
+__device__ __forceinline__ void row_norm_produce(const RowNormArgs& a, int row, int t, int G, int grp,
+                                                 vec16 (&yv)[VPT]) {
     __shared__ double red[GROUPS][32];
     const bool have = row < a.rows;
     const size_t roff = (size_t)(have ? row : 0) * (size_t)a.nvec;
@@ -115,12 +119,21 @@ __device__ __forceinline__ void row_norm_body(const RowNormArgs& a, int row, int
     const int nwarps = G >> 5;
     for (int w = 0; w < nwarps; w++) ss += red[grp][w];
     const float inv = inv_rms(ss, a.hidden, a.eps);
+#pragma unroll
+    for (int j = 0; j < VPT; j++) yv[j] = scale_row_vec(hv[j], wv[j], inv);
+}
 
-    vec16* np_ = a.normed + roff;
+/* One row: produce, then stream the normalised row out. */
+template <int VPT, int GROUPS>
+__device__ __forceinline__ void row_norm_body(const RowNormArgs& a, int row, int t, int G, int grp) {
+    vec16 yv[VPT];
+    row_norm_produce<VPT, GROUPS>(a, row, t, G, grp, yv);
+    if (row >= a.rows) return;
+    vec16* np_ = a.normed + (size_t)row * (size_t)a.nvec;
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
         const int v = t + j * G;
-        if (v < nvec) st_stream(np_ + v, scale_row_vec(hv[j], wv[j], inv));
+        if (v < a.nvec) st_stream(np_ + v, yv[j]);
     }
 }
 

@@ -46,6 +46,15 @@ int vvbk_layer_chain(void* hidden, const void* delta, const void* weight, void* 
                      int rows, int hidden_size, int n_q_heads, int n_kv_heads, int head_dim,
                      int inter, int position_offset, const float* inv_freq, float eps, void* stream);
 
+/* Per-token int8 activation quantizers (csrc/act_quant.cu).
+ *   mode 0: a = x                         -> xq, sx, xsum
+ *   mode 1: RMSNorm of a (+ delta b, the updated row written to row_out) -> ...
+ *   mode 2: SwiGLU of a = gate, b = up    -> ...
+ * K a multiple of 32, pointers 16-byte aligned, layout 0..3. */
+int vvbk_act_quant(int mode, const void* a, const void* b, const void* weight, void* row_out,
+                   int M, int K, float eps, int layout,
+                   int8_t* xq, float* sx, int32_t* xsum, void* stream);
+
 /* Flat elementwise ops (csrc/elementwise.cu). */
 int vvbk_residual_add(void* x, const void* y, size_t n, void* stream);
 int vvbk_bias_add(void* out, const void* bias, int M, int N, void* stream);

@@ -180,6 +180,58 @@ vv_status_t vvb_layer_chain_dev(const vvb_layer_chain_t* c, void* stream) {
     return vvb_swiglu_dev(c->gate, c->up, c->gate, (size_t)c->rows * (size_t)c->inter, stream);
 }
 
+/* --------------------------------------------------- int8 activation quantizers */
+
+/* The reference's argument checks, in its order (src/cuda/act_quant.cu:222-233):
+ * NULL tensors, then M/K <= 0, then K % 32 / K too wide. */
+static vv_status_t q8_check(int M, int K, const void* a, const int8_t* xq, const float* sx) {
+    if (!a || !xq || !sx) return VV_ERR_NULL_PTR;
+    if (M <= 0 || K <= 0) return VV_ERR_INVALID_ARG;
+    if ((K & 31) != 0 || K > VV_ACT_QUANT_MAX_K) return VV_ERR_UNSUPPORTED;
+    return VV_OK;
+}
+
+static int q8_aligned(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+vv_status_t vv_act_quant_dev(const void* x, int M, int K, int layout,
+                             int8_t* xq, float* sx, int32_t* xsum, void* stream) {
+    vv_status_t st = q8_check(M, K, x, xq, sx);
+    if (st != VV_OK) return st;
+    if (layout < 0 || layout >= VV_Q8_LAYOUT_COUNT) return VV_ERR_INVALID_ARG;
+    if (!q8_aligned(x) || !q8_aligned(xq)) return VV_ERR_UNSUPPORTED;
+    return from_cuda(vvbk_act_quant(0, x, NULL, NULL, NULL, M, K, 0.0f, layout, xq, sx, xsum, stream));
+}
+
+vv_status_t vvb_add_rmsnorm_q8_dev(void* hidden_inout, const void* delta, const void* weight,
+                                   int M, int K, float eps, int layout,
+                                   int8_t* xq, float* sx, int32_t* xsum, void* stream) {
+    vv_status_t st = q8_check(M, K, hidden_inout, xq, sx);
+    if (st != VV_OK) return st;
+    if (!weight) return VV_ERR_NULL_PTR;
+    if (layout < 0 || layout >= VV_Q8_LAYOUT_COUNT) return VV_ERR_INVALID_ARG;
+    if (K < VV_ACT_QUANT_MIN_K) return VV_ERR_UNSUPPORTED;
+    if (!q8_aligned(hidden_inout) || !q8_aligned(delta) || !q8_aligned(weight) || !q8_aligned(xq))
+        return VV_ERR_UNSUPPORTED;
+    return from_cuda(vvbk_act_quant(1, hidden_inout, delta, weight, delta ? hidden_inout : NULL,
+                                    M, K, eps, layout, xq, sx, xsum, stream));
+}
+
+vv_status_t vv_rmsnorm_q8_dev(const void* x, const void* weight, int M, int K, float eps,
+                              int layout, int8_t* xq, float* sx, int32_t* xsum, void* stream) {
+    /* no addend: the row is only read */
+    return vvb_add_rmsnorm_q8_dev((void*)(uintptr_t)x, NULL, weight, M, K, eps, layout, xq, sx, xsum, stream);
+}
+
+vv_status_t vv_swiglu_q8_dev(const void* gate, const void* up, int M, int K, int layout,
+                             int8_t* xq, float* sx, int32_t* xsum, void* stream) {
+    vv_status_t st = q8_check(M, K, gate, xq, sx);
+    if (st != VV_OK) return st;
+    if (!up) return VV_ERR_NULL_PTR;
+    if (layout < 0 || layout >= VV_Q8_LAYOUT_COUNT) return VV_ERR_INVALID_ARG;
+    if (!q8_aligned(gate) || !q8_aligned(up) || !q8_aligned(xq)) return VV_ERR_UNSUPPORTED;
+    return from_cuda(vvbk_act_quant(2, gate, up, NULL, NULL, M, K, 0.0f, layout, xq, sx, xsum, stream));
+}
+
 /* ------------------------------------------------------------ introspection */
 
 const char* vvb_version(void) { return "vvb200 " VVB_VERSION " sm_100a"; }

@@ -70,6 +70,10 @@ SIGNATURES = {
     "vv_bias_add_dev": (_i, [_vp, _vp, _i, _i, _vp]),
     "vv_fp32_to_fp16_dev": (_i, [_vp, _vp, _i, _vp]),
     "vv_fp16_to_fp32_dev": (_i, [_vp, _vp, _i, _vp]),
+    "vv_act_quant_dev": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "vv_rmsnorm_q8_dev": (_i, [_vp, _vp, _i, _i, _f, _i, _vp, _vp, _vp, _vp]),
+    "vv_swiglu_q8_dev": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "vvb_add_rmsnorm_q8_dev": (_i, [_vp, _vp, _vp, _i, _i, _f, _i, _vp, _vp, _vp, _vp]),
     "vvb_add_rmsnorm_dev": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
     "vvb_rope_qk_dev": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp]),
     "vvb_embedding_rmsnorm_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
@@ -164,6 +168,30 @@ def vv_fp32_to_fp16_dev(in_fp32, out_fp16, n, stream=None) -> int:
 
 def vv_fp16_to_fp32_dev(in_fp16, out_fp32, n, stream=None) -> int:
     return _lib.vv_fp16_to_fp32_dev(_ptr(in_fp16), _ptr(out_fp32), n, _stream(stream))
+
+
+# per-token int8 activations (include/vibevoice/device.h:297-331)
+VV_Q8_NATURAL, VV_Q8_NIBBLE, VV_Q8_W4_GEMV, VV_Q8_W4_MMA = 0, 1, 2, 3
+VV_ACT_QUANT_MAX_K, VV_ACT_QUANT_MIN_K = 22528, 256
+
+
+def vv_act_quant_dev(x, M, K, layout, xq, sx, xsum, stream=None) -> int:
+    return _lib.vv_act_quant_dev(_ptr(x), M, K, layout, _ptr(xq), _ptr(sx), _ptr(xsum), _stream(stream))
+
+
+def vv_rmsnorm_q8_dev(x, weight, M, K, eps, layout, xq, sx, xsum, stream=None) -> int:
+    return _lib.vv_rmsnorm_q8_dev(_ptr(x), _ptr(weight), M, K, eps, layout, _ptr(xq), _ptr(sx), _ptr(xsum),
+                                  _stream(stream))
+
+
+def vv_swiglu_q8_dev(gate, up, M, K, layout, xq, sx, xsum, stream=None) -> int:
+    return _lib.vv_swiglu_q8_dev(_ptr(gate), _ptr(up), M, K, layout, _ptr(xq), _ptr(sx), _ptr(xsum),
+                                 _stream(stream))
+
+
+def vvb_add_rmsnorm_q8_dev(hidden_inout, delta, weight, M, K, eps, layout, xq, sx, xsum, stream=None) -> int:
+    return _lib.vvb_add_rmsnorm_q8_dev(_ptr(hidden_inout), _ptr(delta), _ptr(weight), M, K, eps, layout,
+                                       _ptr(xq), _ptr(sx), _ptr(xsum), _stream(stream))
 
 
 # ------------------------------------------------------------------ group 2
