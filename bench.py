@@ -451,6 +451,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
     ap.add_argument("--rows", type=int, default=T_TOTAL,
                     help="token rows in total (default: the named config's 14449; smaller for profiler captures)")
+    ap.add_argument("--workload", choices=["chain", "kernels"], default="chain",
+                    help="chain: the benchmark line (config 5); kernels: one line of per-kernel timings at the "
+                         "shapes of configs 1-4 and for the int8 activation quantizers (1 GPU)")
     ap.add_argument("--cpu-baseline-worker", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
 
@@ -463,6 +466,12 @@ def main():
         sys.exit(subprocess.call(cmd))
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.workload == "kernels":
+        import torch
+        assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+        torch.cuda.set_device(0)
+        from vvb200 import kernel_bench
+        return kernel_bench.main(*measured_hbm_peak())
     return run_native(args)
 
 

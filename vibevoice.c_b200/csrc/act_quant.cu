@@ -79,14 +79,16 @@ act_quant_kernel(const ActQuantArgs a) {
     }
 
     /* 2. absolute maximum of the row */
-    float amax = 0.0f;
+    /* the maximum of FP16 magnitudes is itself an FP16 value: take it with
+     * packed half2 max (two elements per instruction), widen once */
+    __half2 m2 = __float2half2_rn(0.0f);
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
-        float f[8];
-        unpack8(yv[j], f);
+        const __half2* h2 = reinterpret_cast<const __half2*>(&yv[j]);
 #pragma unroll
-        for (int e = 0; e < 8; e++) amax = fmaxf(amax, fabsf(f[e]));
+        for (int e = 0; e < 4; e++) m2 = __hmax2(m2, __habs2(h2[e]));
     }
+    float amax = fmaxf(__low2float(m2), __high2float(m2));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if ((t & 31) == 0) red_max[t >> 5] = amax;
@@ -109,17 +111,21 @@ act_quant_kernel(const ActQuantArgs a) {
         const bool ok = v < a.nvec;
         float f[8];
         unpack8(yv[j], f);
-        int s = 0;
-        uint32_t lo = 0, hi = 0;
+        /* round-half-even without the conversion unit: p = v*inv is rounded
+         * to float first (as the CPU does) and adding 1.5*2^23 rounds it to an
+         * integer in the float adder's nearest-even mode; the low byte of the
+         * sum's bit pattern is then q as a signed byte (the constant's low
+         * byte is zero). The reference's clamp to +-127 can never act: amax is
+         * the exact maximum of |v|, so |p| <= amax * fl(127/amax) <
+         * 127.00002 and rounds to at most 127. (Rows holding an infinity or
+         * a NaN have no defined quantization on the CPU path either.) */
+        uint32_t rb[8];
 #pragma unroll
-        for (int e = 0; e < 8; e++) {
-            int q = __float2int_rn(__fmul_rn(f[e], inv));
-            q = max(-127, min(127, q));
-            s += q;
-            const uint32_t byte = (uint32_t)(q & 0xFF);
-            if (e < 4) lo |= byte << (8 * e);
-            else hi |= byte << (8 * (e - 4));
-        }
+        for (int e = 0; e < 8; e++)
+            rb[e] = __float_as_uint(__fadd_rn(__fmul_rn(f[e], inv), 12582912.0f));
+        const uint32_t lo = __byte_perm(__byte_perm(rb[0], rb[1], 0x0040), __byte_perm(rb[2], rb[3], 0x0040), 0x5410);
+        const uint32_t hi = __byte_perm(__byte_perm(rb[4], rb[5], 0x0040), __byte_perm(rb[6], rb[7], 0x0040), 0x5410);
+        int s = __dp4a((int)lo, 0x01010101, __dp4a((int)hi, 0x01010101, 0));   /* sum of the 8 signed bytes */
         if (ok) {
             int8_t* run = xq + ((size_t)(v >> 2) << 5);
             const int i = v & 3;

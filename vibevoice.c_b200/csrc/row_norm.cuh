@@ -47,6 +47,7 @@ template <int VPT, int GROUPS>
 __device__ __forceinline__ void row_norm_produce(const RowNormArgs& a, int row, int t, int G, int grp,
                                                  vec16 (&yv)[VPT]) {
     __shared__ double red[GROUPS][32];
+    __shared__ float inv_s[GROUPS];
     const bool have = row < a.rows;
     const size_t roff = (size_t)(have ? row : 0) * (size_t)a.nvec;
     const int nvec = have ? a.nvec : 0;          /* a group without a row loads and stores nothing */
@@ -113,12 +114,21 @@ __device__ __forceinline__ void row_norm_produce(const RowNormArgs& a, int row, 
     } else {
         asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "r"(G) : "memory");
     }
-    /* every thread adds the warp sums in the same order: one barrier, and all
-     * threads hold the same total */
-    ss = 0.0;
-    const int nwarps = G >> 5;
-    for (int w = 0; w < nwarps; w++) ss += red[grp][w];
-    const float inv = inv_rms(ss, a.hidden, a.eps);
+    /* The scalar tail (a double division, a square root and a float division:
+     * ~130 instructions) is issued by ONE warp of the group, not by all of
+     * them: with 32 elements per thread, every warp repeating it would cost a
+     * third of the kernel's instruction issue. */
+    if (t < 32) {
+        double s = (t < (G >> 5)) ? red[grp][t] : 0.0;
+        s = warp_sum(s);
+        if (t == 0) inv_s[grp] = inv_rms(s, a.hidden, a.eps);
+    }
+    if (GROUPS == 1) {
+        __syncthreads();
+    } else {
+        asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "r"(G) : "memory");
+    }
+    const float inv = inv_s[grp];
 #pragma unroll
     for (int j = 0; j < VPT; j++) yv[j] = scale_row_vec(hv[j], wv[j], inv);
 }

@@ -1,0 +1,132 @@
+"""Per-kernel timings at the BASELINE shapes (configs 1-4) and for the int8
+activation quantizers: `python bench.py --workload kernels`.
+
+Each case is launched `iters` times from one CUDA graph over rotating buffer
+sets whose total size exceeds 2.5x the L2 (so every launch reads cold HBM even
+when one set would fit in the cache), timed with CUDA events on the replaying
+stream; the figure is the best of three replays divided by `iters`. A second
+figure, `warm_us`, replays over a single buffer set (L2-resident for the small
+shapes) and is the launch latency a decode step sees; it is never reported as
+HBM bandwidth.
+"""
+from __future__ import annotations
+
+import json
+
+import torch
+
+import vvb200 as vv
+
+H, NQ, NKV, HD, INTER, VOCAB = 3584, 28, 4, 128, 18944, 151936
+L2_BYTES = 126e6
+
+
+def _time_graph(fn, nsets, iters):
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for i in range(min(nsets, 3)):
+            fn(i % nsets, s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for i in range(iters):
+                fn(i % nsets, s)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = float("inf")
+        for _ in range(3):
+            e0.record(s)
+            g.replay()
+            e1.record(s)
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) * 1e3 / iters)
+    return best
+
+
+def _nsets(bytes_per_set):
+    return max(1, min(48, int(2.5 * L2_BYTES / bytes_per_set) + 1))
+
+
+def _case(name, make_set, call, set_bytes, algo_bytes, peak, iters=40):
+    ns = _nsets(set_bytes)
+    sets = [make_set() for _ in range(ns)]
+    cold = _time_graph(lambda i, s: call(sets[i], s), ns, iters)
+    warm = _time_graph(lambda i, s: call(sets[0], s), 1, iters)
+    gbs = algo_bytes / cold / 1e3
+    del sets
+    torch.cuda.empty_cache()
+    return {"case": name, "us": round(cold, 2), "GB/s": round(gbs, 1), "frac_of_peak": round(gbs / peak, 3),
+            "algorithmic_bytes": algo_bytes, "buffer_sets": ns, "warm_us": round(warm, 2)}
+
+
+def run(peak_gbs: float, peak_kind: str):
+    dev = torch.device("cuda", torch.cuda.current_device())
+    rn = lambda *s: torch.randn(*s, device=dev).half()
+    w = (1 + 0.02 * torch.randn(H, device=dev)).half()
+    out = []
+
+    def ok(st):
+        assert st == 0, st
+
+    # config 1: add + RMSNorm [512, 3584]
+    for rows in (512, 4096):
+        out.append(_case(
+            f"add_rmsnorm [{rows},3584]", lambda: (rn(rows, H), rn(rows, H), torch.empty(rows, H, device=dev, dtype=torch.float16)),
+            lambda b, s: ok(vv.vvb_add_rmsnorm_dev(b[0], b[1], w, b[2], rows, H, 1e-6, s)),
+            rows * H * 2 * 3, rows * H * 2 * 4 + 2 * H, peak_gbs))
+    # config 2: RoPE prefill, Q [4096,28,128] + K [4096,4,128]
+    rows = 4096
+    out.append(_case(
+        "rope_qk [4096,28+4,128]", lambda: (rn(rows, NQ, HD), rn(rows, NKV, HD)),
+        lambda b, s: ok(vv.vvb_rope_qk_dev(b[0], b[1], rows, NQ, NKV, HD, 0, None, 1e6, s)),
+        rows * (NQ + NKV) * HD * 2, 2 * rows * (NQ + NKV) * HD * 2, peak_gbs))
+    # config 3: SwiGLU [4096,18944] and the decode shape [64,18944], in place on gate
+    for rows in (4096, 64):
+        out.append(_case(
+            f"swiglu [{rows},18944]", lambda: (rn(rows, INTER), rn(rows, INTER)),
+            lambda b, s: ok(vv.vvb_swiglu_dev(b[0], b[1], b[0], rows * INTER, s)),
+            rows * INTER * 2 * 2, rows * INTER * 2 * 3, peak_gbs))
+    # config 4: gather 16384 rows of [151936, 3584] + RMSNorm (fused), and the plain gather
+    rows = 16384
+    table = torch.empty(VOCAB, H, device=dev, dtype=torch.float16).normal_(0, 0.02)
+    mk_ids = lambda: torch.randint(0, VOCAB, (rows,), device=dev, dtype=torch.int32)
+    out.append(_case(
+        "embedding_rmsnorm 16384 of [151936,3584]",
+        lambda: (mk_ids(), torch.empty(rows, H, device=dev, dtype=torch.float16), torch.empty(rows, H, device=dev, dtype=torch.float16)),
+        lambda b, s: ok(vv.vvb_embedding_rmsnorm_dev(table, b[0], b[1], w, b[2], rows, H, VOCAB, 1e-6, s)),
+        rows * H * 2 * 3, rows * H * 2 * 3 + rows * 4 + 2 * H, peak_gbs, iters=20))
+    out.append(_case(
+        "embedding 16384 of [151936,3584]",
+        lambda: (mk_ids(), torch.empty(rows, H, device=dev, dtype=torch.float16)),
+        lambda b, s: ok(vv.vv_embedding_dev(table, b[0], b[1], rows, H, s)),
+        rows * H * 2 * 2, rows * H * 2 * 2 + rows * 4, peak_gbs, iters=20))
+    del table
+    torch.cuda.empty_cache()
+    # int8 activation quantizers at long-prompt prefill size (14449 rows), with run sums
+    rows = 14449
+
+    def qbufs(K):
+        return (torch.empty(rows, K, device=dev, dtype=torch.int8), torch.empty(rows, device=dev, dtype=torch.float32),
+                torch.empty(rows, K // 32, device=dev, dtype=torch.int32))
+
+    qout = lambda K: rows * (K + 4 + K // 8)
+    for layout, lname in ((0, "natural"), (3, "w4_mma")):
+        out.append(_case(
+            f"rmsnorm_q8 [14449,3584] {lname}", lambda: (rn(rows, H),) + qbufs(H),
+            lambda b, s: ok(vv.vv_rmsnorm_q8_dev(b[0], w, rows, H, 1e-6, layout, b[1], b[2], b[3], s)),
+            rows * H * 2 + qout(H), rows * H * 2 + 2 * H + qout(H), peak_gbs))
+        out.append(_case(
+            f"swiglu_q8 [14449,18944] {lname}", lambda: (rn(rows, INTER), rn(rows, INTER)) + qbufs(INTER),
+            lambda b, s: ok(vv.vv_swiglu_q8_dev(b[0], b[1], rows, INTER, layout, b[2], b[3], b[4], s)),
+            rows * INTER * 4 + qout(INTER), rows * INTER * 4 + qout(INTER), peak_gbs, iters=20))
+    out.append(_case(
+        "act_quant [14449,3584] natural", lambda: (rn(rows, H),) + qbufs(H),
+        lambda b, s: ok(vv.vv_act_quant_dev(b[0], rows, H, 0, b[1], b[2], b[3], s)),
+        rows * H * 2 + qout(H), rows * H * 2 + qout(H), peak_gbs))
+    return {"workload": "kernels", "peak_GB/s": peak_gbs, "peak_kind": "of " + peak_kind,
+            "method": "CUDA-graph replay over rotating buffer sets > 2.5x L2, CUDA events, best of 3", "cases": out}
+
+
+def main(peak_gbs, peak_kind):
+    print(json.dumps(run(peak_gbs, peak_kind)), flush=True)
