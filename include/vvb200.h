@@ -148,6 +148,13 @@ vv_status_t vv_rmsnorm_q8_dev(const void* x, const void* weight, int M, int K, f
 vv_status_t vv_swiglu_q8_dev(const void* gate, const void* up, int M, int K, int layout,
                              int8_t* xq, float* sx, int32_t* xsum, void* stream);
 
+/** Calibration statistics: acc[k] = max(acc[k], max over rows of |x[m,k]|),
+ *  x FP16 [M,K], acc FP32 [K] in device memory holding non-negative values,
+ *  updated in place (exact in any order). Replaces
+ *  include/vibevoice/device.h:333-342 (src/cuda/act_quant.cu:303): with it this
+ *  library defines every symbol of the reference's act_quant.cu. */
+vv_status_t vv_col_absmax_dev(const void* x, int M, int K, float* acc, void* stream);
+
 /* ====================================================================== *
  *  Group 2 -- additive entry points (no counterpart symbol in the          *
  *  reference; each states the reference call sequence it equals)           *

@@ -154,6 +154,28 @@ def test_q8_kernels_equal_oracle_and_unfused(vv, orc, M, K):
 
 
 @gpu
+@pytest.mark.parametrize("M,K", [(1, 3584), (285, 3584), (1000, 18944), (37, 1536), (5, 250), (70, 7)])
+def test_col_absmax(vv, M, K):
+    """acc[k] = max(acc[k], max_m |x[m,k]|) (tests/test_int8_linear.c:370-395
+    checks it against a host loop): exact, and it accumulates over calls."""
+    rng = np.random.default_rng(M + K)
+    x1 = (rng.standard_normal((M, K)) * 3).astype(np.float16)
+    x2 = (rng.standard_normal((M, K)) * 3).astype(np.float16)
+    acc = torch.zeros(K + 64, dtype=torch.float32, device="cuda")
+    acc[K:] = -5.0                                               # canary: never touched
+    assert vv.vv_col_absmax_dev(dev(x1), M, K, acc) == 0
+    torch.cuda.synchronize()
+    want1 = np.abs(x1.astype(np.float32)).max(axis=0)
+    assert np.array_equal(acc[:K].cpu().numpy(), want1)
+    assert vv.vv_col_absmax_dev(dev(x2), M, K, acc) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(acc[:K].cpu().numpy(), np.maximum(want1, np.abs(x2.astype(np.float32)).max(axis=0)))
+    assert (acc[K:].cpu().numpy() == -5.0).all()
+    assert vv.vv_col_absmax_dev(None, M, K, acc) == vv.VV_ERR_NULL_PTR
+    assert vv.vv_col_absmax_dev(dev(x1), 0, K, acc) == vv.VV_ERR_INVALID_ARG
+
+
+@gpu
 def test_q8_argument_checks(vv):
     """src/cuda/act_quant.cu:222-233: NULL -> NULL_PTR, M or K <= 0 ->
     INVALID_ARG, K % 32 != 0 or K > 22528 -> UNSUPPORTED, bad layout ->

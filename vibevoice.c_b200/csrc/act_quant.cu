@@ -151,6 +151,62 @@ act_quant_kernel(const ActQuantArgs a) {
     }
 }
 
+/* Calibration statistics: acc[k] = max(acc[k], max over rows of |x[m,k]|)
+ * (include/vibevoice/device.h:333-342, src/cuda/act_quant.cu:283-300). A thread
+ * owns 8 columns (one vector) over a block of kColRows rows, keeps the running
+ * maximum as packed halves, and merges with an integer atomicMax on the float
+ * bit pattern: the values are non-negative, so float order is integer order
+ * and the result is exact in any order. NaNs never win (hmax2 returns the
+ * other operand), as in the reference. */
+constexpr int kColThreads = 128;
+constexpr int kColRows = 32;
+
+__global__ void __launch_bounds__(kColThreads)
+col_absmax_kernel(const vec16* __restrict__ x, int M, int nvec, float* __restrict__ acc) {
+    const int v = blockIdx.x * kColThreads + threadIdx.x;
+    if (v >= nvec) return;
+    const int m0 = blockIdx.y * kColRows;
+    const int m1 = min(M, m0 + kColRows);
+    __half2 mx[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) mx[e] = __float2half2_rn(0.0f);
+    int m = m0;
+    for (; m + 4 <= m1; m += 4) {
+        vec16 r[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) r[u] = ld_stream(x + (size_t)(m + u) * (size_t)nvec + v);
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const __half2* h2 = reinterpret_cast<const __half2*>(&r[u]);
+#pragma unroll
+            for (int e = 0; e < 4; e++) mx[e] = __hmax2(mx[e], __habs2(h2[e]));
+        }
+    }
+    for (; m < m1; m++) {
+        const vec16 r = ld_stream(x + (size_t)m * (size_t)nvec + v);
+        const __half2* h2 = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+        for (int e = 0; e < 4; e++) mx[e] = __hmax2(mx[e], __habs2(h2[e]));
+    }
+    int* out = reinterpret_cast<int*>(acc) + (size_t)v * 8u;
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        atomicMax(out + 2 * e, __float_as_int(__low2float(mx[e])));
+        atomicMax(out + 2 * e + 1, __float_as_int(__high2float(mx[e])));
+    }
+}
+
+__global__ void __launch_bounds__(256)
+col_absmax_scalar_kernel(const __half* __restrict__ x, int M, int K, float* __restrict__ acc) {
+    const int k = blockIdx.x * 256 + threadIdx.x;
+    if (k >= K) return;
+    const int m0 = blockIdx.y * 64;
+    const int m1 = min(M, m0 + 64);
+    float v = 0.0f;
+    for (int m = m0; m < m1; m++) v = fmaxf(v, fabsf(__half2float(x[(size_t)m * (size_t)K + k])));
+    if (v == v) atomicMax(reinterpret_cast<int*>(acc) + k, __float_as_int(v));
+}
+
 template <int MODE>
 static cudaError_t launch_q(const ActQuantArgs& a, cudaStream_t s) {
     int threads = (((a.nvec + 3) / 4) + 31) / 32 * 32;
@@ -192,4 +248,21 @@ extern "C" int vvbk_act_quant(int mode, const void* a, const void* b, const void
     if (mode == Q_RMSNORM) return (int)launch_q<Q_RMSNORM>(q, s);
     if (mode == Q_SWIGLU) return (int)launch_q<Q_SWIGLU>(q, s);
     return (int)launch_q<Q_PLAIN>(q, s);
+}
+
+extern "C" int vvbk_col_absmax(const void* x, int M, int K, float* acc, void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (K % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+        const int nvec = K / 8;
+        const dim3 grid((unsigned)((nvec + kColThreads - 1) / kColThreads),
+                        (unsigned)((M + kColRows - 1) / kColRows));
+        if (grid.y > 65535u) return (int)cudaErrorInvalidValue;
+        col_absmax_kernel<<<grid, kColThreads, 0, s>>>((const vec16*)x, M, nvec, acc);
+    } else {
+        const dim3 grid((unsigned)((K + 255) / 256), (unsigned)((M + 63) / 64));
+        if (grid.y > 65535u) return (int)cudaErrorInvalidValue;
+        col_absmax_scalar_kernel<<<grid, 256, 0, s>>>((const __half*)x, M, K, acc);
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return (int)cudaGetLastError();
 }

@@ -55,6 +55,9 @@ int vvbk_act_quant(int mode, const void* a, const void* b, const void* weight, v
                    int M, int K, float eps, int layout,
                    int8_t* xq, float* sx, int32_t* xsum, void* stream);
 
+/* acc[k] = max(acc[k], max_m |x[m,k]|), x FP16 [M,K], acc FP32 [K] (csrc/act_quant.cu). */
+int vvbk_col_absmax(const void* x, int M, int K, float* acc, void* stream);
+
 /* Flat elementwise ops (csrc/elementwise.cu). */
 int vvbk_residual_add(void* x, const void* y, size_t n, void* stream);
 int vvbk_bias_add(void* out, const void* bias, int M, int N, void* stream);

@@ -232,6 +232,12 @@ vv_status_t vv_swiglu_q8_dev(const void* gate, const void* up, int M, int K, int
     return from_cuda(vvbk_act_quant(2, gate, up, NULL, NULL, M, K, 0.0f, layout, xq, sx, xsum, stream));
 }
 
+vv_status_t vv_col_absmax_dev(const void* x, int M, int K, float* acc, void* stream) {
+    if (!x || !acc) return VV_ERR_NULL_PTR;
+    if (M <= 0 || K <= 0) return VV_ERR_INVALID_ARG;
+    return from_cuda(vvbk_col_absmax(x, M, K, acc, stream));
+}
+
 /* ------------------------------------------------------------ introspection */
 
 const char* vvb_version(void) { return "vvb200 " VVB_VERSION " sm_100a"; }

@@ -74,6 +74,7 @@ SIGNATURES = {
     "vv_rmsnorm_q8_dev": (_i, [_vp, _vp, _i, _i, _f, _i, _vp, _vp, _vp, _vp]),
     "vv_swiglu_q8_dev": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "vvb_add_rmsnorm_q8_dev": (_i, [_vp, _vp, _vp, _i, _i, _f, _i, _vp, _vp, _vp, _vp]),
+    "vv_col_absmax_dev": (_i, [_vp, _i, _i, _vp, _vp]),
     "vvb_add_rmsnorm_dev": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
     "vvb_rope_qk_dev": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp]),
     "vvb_embedding_rmsnorm_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
@@ -192,6 +193,10 @@ def vv_swiglu_q8_dev(gate, up, M, K, layout, xq, sx, xsum, stream=None) -> int:
 def vvb_add_rmsnorm_q8_dev(hidden_inout, delta, weight, M, K, eps, layout, xq, sx, xsum, stream=None) -> int:
     return _lib.vvb_add_rmsnorm_q8_dev(_ptr(hidden_inout), _ptr(delta), _ptr(weight), M, K, eps, layout,
                                        _ptr(xq), _ptr(sx), _ptr(xsum), _stream(stream))
+
+
+def vv_col_absmax_dev(x, M, K, acc, stream=None) -> int:
+    return _lib.vv_col_absmax_dev(_ptr(x), M, K, _ptr(acc), _stream(stream))
 
 
 # ------------------------------------------------------------------ group 2
