@@ -52,6 +52,35 @@ def test_header_compiles_as_c11_and_cxx(tmp_path):
                     str(tmp_path / "t2.o")], check=True)
 
 
+REF_INCLUDE = os.environ.get("VV_REFERENCE_DIR", "/root/reference") + "/include"
+
+
+@pytest.mark.skipif(not os.path.exists(REF_INCLUDE + "/vibevoice/device.h"), reason="reference headers not mounted")
+def test_declarations_agree_with_the_reference_headers(tmp_path):
+    """One translation unit includes the reference's own device.h and then
+    vvb200.h: a C compiler rejects any redeclaration whose type differs, so this
+    compiles only if every drop-in signature (and the status enum it returns)
+    is the reference's. The unit also takes each function's address through the
+    reference's prototype and links against the static archive."""
+    names = ["vv_embedding_dev", "vv_rmsnorm_dev", "vv_rope_dev", "vv_swiglu_dev", "vv_swiglu_fused_dev",
+             "vv_residual_add_dev", "vv_bias_add_dev", "vv_fp32_to_fp16_dev", "vv_fp16_to_fp32_dev",
+             "vv_act_quant_dev", "vv_rmsnorm_q8_dev", "vv_swiglu_q8_dev", "vv_col_absmax_dev"]
+    src = tmp_path / "both.c"
+    src.write_text('#include "vibevoice/device.h"\n#include "vvb200.h"\n#include <stdio.h>\n'
+                   "int main(void) {\n  const void* fns[] = {" + ", ".join(f"(const void*){n}" for n in names) +
+                   "};\n  printf(\"%d\\n\", (int)(sizeof fns / sizeof fns[0]));\n"
+                   "  return VV_Q8_LAYOUT_COUNT == 4 && VV_ACT_QUANT_MAX_K == 22528 && VV_ERR_CUDA_LAUNCH == -102 ? 0 : 1;\n}\n")
+    obj = tmp_path / "both.o"
+    subprocess.run(["gcc", "-std=c11", "-Wall", "-Werror", f"-I{REF_INCLUDE}", f"-I{ROOT}/include", "-c", str(src),
+                    "-o", str(obj)], check=True)
+    exe = tmp_path / "both"
+    lib = os.path.join(ROOT, "vibevoice.c_b200", "lib", "libvvb200.a")
+    subprocess.run(["g++", str(obj), lib, "-L/usr/local/cuda/lib64", "-lcudart_static", "-lpthread", "-ldl", "-lrt",
+                    "-lm", "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout
+    assert out.strip() == str(len(names))
+
+
 def test_version_and_status_strings(vv):
     assert vv.version().startswith("vvb200 ") and "sm_100a" in vv.version()
     assert vv.status_string(0) == "ok"
