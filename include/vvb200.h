@@ -184,6 +184,27 @@ vv_status_t vvb_rope_qk_dev(void* q, void* k, int rows, int n_q_heads, int n_kv_
                             int head_dim, int position_offset, const int* d_position,
                             float theta, void* stream);
 
+/** The projections' bias adds, RoPE on Q and K, and the KV-cache append of one
+ *  layer in ONE launch: q = rope(f16(q + q_bias)) in place; the cache row
+ *  (cache_offset + r) of k_cache receives rope(f16(k[r] + k_bias)) and that of
+ *  v_cache receives f16(v[r] + v_bias). Replaces up to six passes of the
+ *  reference: vv_bias_add_dev x3 (src/inference/decoder.c:463-464), vv_rope_dev
+ *  x2 (:850-855) and the two device copies of vv_kv_cache_append for the raw
+ *  FP16 cache (src/inference/kv_cache.c:229-246). k_cache and v_cache are one
+ *  layer's [max_len, n_kv_heads * head_dim] FP16 arrays; the caller guarantees
+ *  cache_offset + rows <= max_len. Each bias may be NULL. When d_position is
+ *  non-NULL the device int gives BOTH the RoPE position and the cache row of
+ *  row 0 (the decode step's kv length, src/inference/decoder.c:735-737).
+ *  keep_k != 0 also writes the rotated K back over k. head_dim must be a
+ *  multiple of 16 and every pointer 16-byte aligned (VV_ERR_UNSUPPORTED
+ *  otherwise: use the separate ops). */
+vv_status_t vvb_rope_qk_append_dev(void* q, void* k, const void* v,
+                                   const void* q_bias, const void* k_bias, const void* v_bias,
+                                   void* k_cache, void* v_cache,
+                                   int rows, int n_q_heads, int n_kv_heads, int head_dim,
+                                   int position_offset, int cache_offset, const int* d_position,
+                                   float theta, int keep_k, void* stream);
+
 /** hidden_out[p] = table[clamp(ids[p], 0, vocab-1)] (bit copy) and
  *  normed_out[p] = rmsnorm(hidden_out[p]) in one kernel: the gather of
  *  src/inference/pipeline.c:2309 fused with layer 0's first norm

@@ -33,6 +33,16 @@ int vvbk_row_norm(const void* src_rows, const void* delta, const int32_t* ids, i
 int vvbk_rope(void* q, void* k, int rows, int n_q_heads, int n_kv_heads, int head_dim,
               int position_offset, const int* d_position, const float* inv_freq, void* stream);
 
+/* Bias add + RoPE + KV-cache append in one launch (csrc/rope_append.cu).
+ * Returns cudaErrorNotSupported (801) without launching when head_dim % 16 != 0
+ * or a pointer is not 16-byte aligned. */
+int vvbk_rope_append(void* q, void* k, const void* v,
+                     const void* q_bias, const void* k_bias, const void* v_bias,
+                     void* k_cache, void* v_cache,
+                     int rows, int n_q_heads, int n_kv_heads, int head_dim,
+                     int position_offset, int cache_offset, const int* d_position,
+                     const float* inv_freq, int keep_k, void* stream);
+
 /* SwiGLU (csrc/swiglu.cu). Flat: gate/up/out of n elements. Fused: rows of
  * [gate | up] with 2*inter halves per row. */
 int vvbk_swiglu(const void* gate, const void* up, void* out, size_t n, void* stream);

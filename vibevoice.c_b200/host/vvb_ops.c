@@ -63,6 +63,26 @@ vv_status_t vvb_rope_qk_dev(void* q, void* k, int rows, int n_q_heads, int n_kv_
                                position_offset, d_position, inv_freq, stream));
 }
 
+vv_status_t vvb_rope_qk_append_dev(void* q, void* k, const void* v,
+                                   const void* q_bias, const void* k_bias, const void* v_bias,
+                                   void* k_cache, void* v_cache,
+                                   int rows, int n_q_heads, int n_kv_heads, int head_dim,
+                                   int position_offset, int cache_offset, const int* d_position,
+                                   float theta, int keep_k, void* stream) {
+    if (!q || !k || !v || !k_cache || !v_cache) return VV_ERR_NULL_PTR;
+    if (rows < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || cache_offset < 0)
+        return VV_ERR_INVALID_ARG;
+    if (rows == 0) return VV_OK;
+    if (head_dim / 2 > VVB_ROPE_MAX_HALF) return VV_ERR_UNSUPPORTED;
+    float inv_freq[VVB_ROPE_MAX_HALF];
+    fill_inv_freq(inv_freq, head_dim, theta);
+    const int err = vvbk_rope_append(q, k, v, q_bias, k_bias, v_bias, k_cache, v_cache, rows,
+                                     n_q_heads, n_kv_heads, head_dim, position_offset, cache_offset,
+                                     d_position, inv_freq, keep_k, stream);
+    if (err == 801) return VV_ERR_UNSUPPORTED;   /* cudaErrorNotSupported: not vectorisable */
+    return from_cuda(err);
+}
+
 vv_status_t vv_rope_dev(void* x, int seq_len, int n_heads, int head_dim,
                         int position_offset, const int* d_position, float theta,
                         void* stream) {

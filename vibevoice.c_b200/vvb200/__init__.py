@@ -78,6 +78,7 @@ SIGNATURES = {
     "vvb_add_rmsnorm_dev": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
     "vvb_rope_qk_dev": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp]),
     "vvb_embedding_rmsnorm_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
+    "vvb_rope_qk_append_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _f, _i, _vp]),
     "vvb_swiglu_dev": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "vvb_residual_add_dev": (_i, [_vp, _vp, _sz, _vp]),
     "vvb_layer_chain_dev": (_i, [C.POINTER(LayerChain), _vp]),
@@ -209,6 +210,14 @@ def vvb_rope_qk_dev(q, k, rows, n_q_heads, n_kv_heads, head_dim, position_offset
                     stream=None) -> int:
     return _lib.vvb_rope_qk_dev(_ptr(q), _ptr(k), rows, n_q_heads, n_kv_heads, head_dim, position_offset,
                                 _ptr(d_position), theta, _stream(stream))
+
+
+def vvb_rope_qk_append_dev(q, k, v, q_bias, k_bias, v_bias, k_cache, v_cache, rows, n_q_heads, n_kv_heads, head_dim,
+                           position_offset, cache_offset, d_position, theta, keep_k=0, stream=None) -> int:
+    return _lib.vvb_rope_qk_append_dev(_ptr(q), _ptr(k), _ptr(v), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
+                                       _ptr(k_cache), _ptr(v_cache), rows, n_q_heads, n_kv_heads, head_dim,
+                                       position_offset, cache_offset, _ptr(d_position), theta, keep_k,
+                                       _stream(stream))
 
 
 def vvb_embedding_rmsnorm_dev(table, ids, hidden_out, weight, normed_out, rows, hidden_size, vocab, eps,

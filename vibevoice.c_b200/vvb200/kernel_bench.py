@@ -81,6 +81,17 @@ def run(peak_gbs: float, peak_kind: str):
         "rope_qk [4096,28+4,128]", lambda: (rn(rows, NQ, HD), rn(rows, NKV, HD)),
         lambda b, s: ok(vv.vvb_rope_qk_dev(b[0], b[1], rows, NQ, NKV, HD, 0, None, 1e6, s)),
         rows * (NQ + NKV) * HD * 2, 2 * rows * (NQ + NKV) * HD * 2, peak_gbs))
+    # bias + RoPE + KV-cache append in one launch (Q in place; K, V read once and written into the cache)
+    rows = 14449
+    bq, bk, bv = rn(NQ * HD), rn(NKV * HD), rn(NKV * HD)
+    out.append(_case(
+        "rope_qk_append [14449,28+4+4,128] with biases",
+        lambda: (rn(rows, NQ, HD), rn(rows, NKV, HD), rn(rows, NKV, HD),
+                 torch.empty(rows, NKV * HD, device=dev, dtype=torch.float16),
+                 torch.empty(rows, NKV * HD, device=dev, dtype=torch.float16)),
+        lambda b, s: ok(vv.vvb_rope_qk_append_dev(b[0], b[1], b[2], bq, bk, bv, b[3], b[4], rows, NQ, NKV, HD, 0, 0,
+                                                  None, 1e6, 0, s)),
+        rows * (NQ + 4 * NKV) * HD * 2, rows * (2 * NQ + 4 * NKV) * HD * 2, peak_gbs))
     # config 3: SwiGLU [4096,18944] and the decode shape [64,18944], in place on gate
     for rows in (4096, 64):
         out.append(_case(
