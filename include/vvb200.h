@@ -155,6 +155,19 @@ vv_status_t vv_swiglu_q8_dev(const void* gate, const void* up, int M, int K, int
  *  library defines every symbol of the reference's act_quant.cu. */
 vv_status_t vv_col_absmax_dev(const void* x, int M, int K, float* acc, void* stream);
 
+/* ---- LM head (the decode step's tail) ---------------------------------- */
+
+/** logits[V] = W[V,K] @ x[K]: FP16 inputs, FP32 accumulation, FP32 output.
+ *  Replaces include/vibevoice/device.h:706-708 (src/cuda/lm_head.cu:127). */
+vv_status_t vv_lm_head_gemv_dev(const void* x, const void* W, void* logits, int V, int K, void* stream);
+
+/** Two-stage argmax over FP32 logits; scratch_v (256 floats) and scratch_i
+ *  (256 ints) are caller-owned device memory, as in the reference. out_value
+ *  may be NULL. Ties go to the smaller index. Replaces
+ *  include/vibevoice/device.h:710-713 (src/cuda/lm_head.cu:161). */
+vv_status_t vv_argmax_dev(const void* logits, int V, void* scratch_v, void* scratch_i,
+                          void* out_token, void* out_value, void* stream);
+
 /* ====================================================================== *
  *  Group 2 -- additive entry points (no counterpart symbol in the          *
  *  reference; each states the reference call sequence it equals)           *
@@ -204,6 +217,21 @@ vv_status_t vvb_rope_qk_append_dev(void* q, void* k, const void* v,
                                    int rows, int n_q_heads, int n_kv_heads, int head_dim,
                                    int position_offset, int cache_offset, const int* d_position,
                                    float theta, int keep_k, void* stream);
+
+/** Final RMSNorm + LM head + greedy argmax in two launches (the reference
+ *  issues four: vv_rmsnorm_dev, vv_lm_head_gemv_dev and vv_argmax_dev's two,
+ *  src/inference/pipeline.c:1962-1978). x[K] is the last hidden row when
+ *  final_norm_w is non-NULL (the norm is applied inside the GEMV's CTAs), else
+ *  the already normalised row. logits (FP32 [V]) may be NULL: the argmax comes
+ *  from per-CTA partials, not from a pass over the logits. scratch is
+ *  caller-owned device memory of at least vvb_lm_head_scratch_bytes(V) bytes,
+ *  4-byte aligned; its contents need no initialisation and are overwritten.
+ *  K must be a multiple of 8 and at most 11264 with 16-byte aligned x, W and
+ *  final_norm_w (VV_ERR_UNSUPPORTED otherwise). out_value may be NULL. */
+size_t vvb_lm_head_scratch_bytes(int V);
+vv_status_t vvb_lm_head_argmax_dev(const void* x, const void* final_norm_w, float eps, const void* W,
+                                   int V, int K, void* logits, void* scratch, size_t scratch_bytes,
+                                   int32_t* out_token, float* out_value, void* stream);
 
 /** hidden_out[p] = table[clamp(ids[p], 0, vocab-1)] (bit copy) and
  *  normed_out[p] = rmsnorm(hidden_out[p]) in one kernel: the gather of

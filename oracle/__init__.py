@@ -120,6 +120,19 @@ class _Restated:
     def threads(self):
         return int(self.lib.orc_threads())
 
+    def lm_head(self, x_f32, w_f16):
+        """(logits float64 [V], token, value) for W[V,K] @ x[K], double accumulation."""
+        L = self.lib
+        L.orc_lm_head.argtypes = [_f32p, _u16p, C.c_int, C.c_int, C.POINTER(C.c_double), _i32p,
+                                  C.POINTER(C.c_double)]
+        V, K = w_f16.shape
+        logits = np.empty(V, np.float64)
+        tok, val = C.c_int32(), C.c_double()
+        st = L.orc_lm_head(_ptr(np.ascontiguousarray(x_f32, dtype=np.float32), _f32p), _ptr(_as_u16(w_f16), _u16p),
+                           V, K, logits.ctypes.data_as(C.POINTER(C.c_double)), C.byref(tok), C.byref(val))
+        assert st == 0, st
+        return logits, int(tok.value), float(val.value)
+
     def quant_act_q8(self, x_f32, layout, want_xsum=True):
         """Per-token int8 quantizer on FP32 rows [M, K]: (xq int8 [M,K],
         sx float32 [M], xsum int32 [M, K/32] or None)."""
@@ -204,6 +217,17 @@ class _Reference:
                                        _ptr(out, _f32p), rows, hidden)
         assert st == 0, st
         return out
+
+    def lm_head_argmax(self, x_f32, w_f16):
+        """vv_lm_head_argmax_cpu (src/cpu/cpu_kernels.c:1570): (token, value)."""
+        L = self.lib
+        L.vv_lm_head_argmax_cpu.argtypes = [_f32p, C.c_void_p, C.c_int, C.c_int, _i32p, _f32p]
+        V, K = w_f16.shape
+        tok, val = C.c_int32(), C.c_float()
+        st = L.vv_lm_head_argmax_cpu(_ptr(np.ascontiguousarray(x_f32, dtype=np.float32), _f32p),
+                                     _as_u16(w_f16).ctypes.data, V, K, C.byref(tok), C.byref(val))
+        assert st == 0, st
+        return int(tok.value), float(val.value)
 
     def threads(self):
         """Sets the OpenMP team to the physical cores and pins it

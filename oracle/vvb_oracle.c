@@ -270,6 +270,33 @@ int orc_swiglu_f16(const uint16_t* gate, const uint16_t* up, uint16_t* out, size
     return ORC_OK;
 }
 
+/* LM head, src/cpu/cpu_kernels.c:1570-1606: logit_t = dot(x, widen(W[t,:])),
+ * token = argmax. The reference sums each dot in FP32 in an order fixed by its
+ * SIMD width (dot_f32, cpu_kernels.c:598-614) and breaks ties by the OpenMP
+ * schedule; this restatement accumulates in DOUBLE (so it is closer to the
+ * exact value than either FP32 order) and takes the first maximum. Tests
+ * compare FP32 implementations with it under a tolerance and demand the same
+ * token whenever the winner's margin exceeds that tolerance. */
+int orc_lm_head(const float* x, const uint16_t* w_f16, int V, int K,
+                double* logits, int32_t* token, double* value) {
+    if (!x || !w_f16 || !logits || !token) return ORC_ERR_NULL_PTR;
+    if (V <= 0 || K <= 0) return ORC_ERR_INVALID_ARG;
+    int t;
+#pragma omp parallel for schedule(static)
+    for (t = 0; t < V; t++) {
+        const uint16_t* row = w_f16 + (size_t)t * (size_t)K;
+        double acc = 0.0;
+        for (int k = 0; k < K; k++) acc += (double)x[k] * (double)orc_half_to_float(row[k]);
+        logits[t] = acc;
+    }
+    int best = 0;
+    for (t = 1; t < V; t++)
+        if (logits[t] > logits[best]) best = t;
+    *token = best;
+    if (value) *value = logits[best];
+    return ORC_OK;
+}
+
 int orc_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -1,0 +1,282 @@
+/*
+ * lm_head.cu -- the decode step's tail: final RMSNorm of the last hidden row,
+ * logits = W[V,K] @ x[K], and the greedy argmax. sm_100a, HBM-bound: the FP16
+ * head of the 7B model is 1.09 GB read once per token
+ * (src/inference/pipeline.c:1962-1986, src/cuda/lm_head.cu:28-96).
+ *
+ *   lm_head_kernel<NORM>   a grid of exactly the CTAs that fit on the GPU at
+ *       once (2 per SM), each owning an equal contiguous block of W's rows, so
+ *       x is staged once per CTA and all CTAs finish together; the 8 warps of
+ *       a CTA take row pairs round-robin, a lane keeping 14 x 2 16-byte loads
+ *       in flight for K = 3584. x sits in shared memory as floats -- with NORM
+ *       the CTA first applies the final RMSNorm to the hidden row (row_norm.cuh's
+ *       arithmetic, rounded to FP16 as vv_rmsnorm_dev would store it), a 7 KB
+ *       L2 read per CTA instead of a separate launch. FP32
+ *       multiply-add per element, warp-shuffle sum, FP32 logit. Each CTA also
+ *       leaves its best (value, index) in a partials array, so the argmax needs
+ *       no pass over the logits.
+ *   argmax_reduce_kernel   one CTA reduces the partials (or 256 of them).
+ *   argmax_logits_kernel   stage 1 of the stand-alone vv_argmax_dev.
+ *
+ * Ties go to the smaller index (the reference's reductions leave ties to the
+ * thread layout, src/cuda/lm_head.cu:65-118; its CPU path to the OpenMP
+ * schedule, src/cpu/cpu_kernels.c:1570-1606).
+ */
+#include "row_norm.cuh"
+#include "vvb_launch.h"
+
+#include <atomic>
+#include <cfloat>
+
+namespace vvb {
+
+extern std::atomic<uint64_t> g_launches;
+
+constexpr int kLmThreads = 256;
+constexpr int kLmMinRowsPerCta = 32;   /* bounds the number of partials: ceil(V / 32) */
+
+struct Best {
+    float v;
+    int i;
+};
+__device__ __forceinline__ Best better(Best a, Best b) {
+    return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+__device__ __forceinline__ Best warp_best(Best b) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other;
+        other.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+        other.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+        b = better(b, other);
+    }
+    return b;
+}
+
+struct LmHeadArgs {
+    const vec16* x;        /* [K] FP16: the normed row, or (NORM) the hidden row */
+    const vec16* norm_w;   /* NORM only */
+    const vec16* W;        /* [V, K] */
+    float* logits;         /* may be null */
+    float* part_v;         /* [gridDim.x] or null */
+    int* part_i;
+    int V, K, nvec;
+    int rows_per_cta;      /* even; gridDim.x * rows_per_cta >= V */
+    float eps;
+};
+
+template <bool NORM>
+__global__ void __launch_bounds__(kLmThreads, 2)
+lm_head_kernel(const LmHeadArgs a) {
+    extern __shared__ __align__(16) float xs[];          /* K floats */
+    __shared__ double red[8];
+    __shared__ float inv_s;
+    __shared__ Best cta_best[8];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+
+    /* stage x (normalised if asked) as floats */
+    if (NORM) {
+        double ss = 0.0;
+        for (int v = t; v < a.nvec; v += kLmThreads) {
+            float f[8];
+            unpack8(__ldg(a.x + v), f);
+#pragma unroll
+            for (int e = 0; e < 8; e++) ss = fma((double)f[e], (double)f[e], ss);
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        if (t < 32) {
+            double s = (t < 8) ? red[t] : 0.0;
+            s = warp_sum(s);
+            if (t == 0) inv_s = inv_rms(s, a.K, a.eps);
+        }
+        __syncthreads();
+        const float inv = inv_s;
+        for (int v = t; v < a.nvec; v += kLmThreads) {
+            float f[8];
+            unpack8(scale_row_vec(__ldg(a.x + v), __ldg(a.norm_w + v), inv), f);   /* rounded to FP16, then widened */
+#pragma unroll
+            for (int e = 0; e < 8; e++) xs[v * 8 + e] = f[e];
+        }
+    } else {
+        for (int v = t; v < a.nvec; v += kLmThreads) {
+            float f[8];
+            unpack8(__ldg(a.x + v), f);
+#pragma unroll
+            for (int e = 0; e < 8; e++) xs[v * 8 + e] = f[e];
+        }
+    }
+    __syncthreads();
+
+    Best best{-FLT_MAX, 0x7fffffff};
+    /* this CTA's contiguous block of rows; its 8 warps take row pairs round-robin */
+    const int cta_lo = blockIdx.x * a.rows_per_cta;
+    const int cta_hi = min(a.V, cta_lo + a.rows_per_cta);
+    for (int r0 = cta_lo + 2 * warp; r0 < cta_hi; r0 += 2 * (kLmThreads / 32)) {
+        const int r1 = r0 + 1;
+        const bool two = r1 < cta_hi;
+        const vec16* w0 = a.W + (size_t)r0 * (size_t)a.nvec;
+        const vec16* w1 = a.W + (size_t)(two ? r1 : r0) * (size_t)a.nvec;
+        float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll 7
+        for (int v = lane; v < a.nvec; v += 32) {
+            const vec16 p0 = ld_stream(w0 + v);
+            const vec16 p1 = ld_stream(w1 + v);
+            const float4 xa = *reinterpret_cast<const float4*>(xs + v * 8);
+            const float4 xb = *reinterpret_cast<const float4*>(xs + v * 8 + 4);
+            float f0[8], f1[8];
+            unpack8(p0, f0);
+            unpack8(p1, f1);
+            const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                acc0 = fmaf(f0[e], xv[e], acc0);
+                acc1 = fmaf(f1[e], xv[e], acc1);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            acc0 += __shfl_xor_sync(0xffffffffu, acc0, o);
+            acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
+        }
+        if (lane == 0) {
+            if (a.logits) {
+                a.logits[r0] = acc0;
+                if (two) a.logits[r1] = acc1;
+            }
+            best = better(best, Best{acc0, r0});
+            if (two) best = better(best, Best{acc1, r1});
+        }
+    }
+    if (a.part_v == nullptr) return;
+    if (lane == 0) cta_best[warp] = best;
+    __syncthreads();
+    if (t == 0) {
+        Best b = cta_best[0];
+#pragma unroll
+        for (int w = 1; w < 8; w++) b = better(b, cta_best[w]);
+        a.part_v[blockIdx.x] = b.v;
+        a.part_i[blockIdx.x] = b.i;
+    }
+}
+
+/* Any K / alignment: one warp per row, scalar halves, x from global memory. */
+__global__ void __launch_bounds__(256)
+lm_head_scalar_kernel(const __half* x, const __half* W, float* logits, int V, int K) {
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= V) return;
+    const int lane = threadIdx.x & 31;
+    const __half* w = W + (size_t)row * (size_t)K;
+    float acc = 0.0f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(__half2float(w[k]), __half2float(x[k]), acc);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) logits[row] = acc;
+}
+
+/* Stage 1 of the stand-alone argmax: gridDim.x partials over FP32 logits. */
+__global__ void __launch_bounds__(256)
+argmax_logits_kernel(const float* __restrict__ logits, int V, float* part_v, int* part_i) {
+    __shared__ Best wb[8];
+    Best best{-FLT_MAX, 0x7fffffff};
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < V; i += gridDim.x * 256)
+        best = better(best, Best{logits[i], i});
+    best = warp_best(best);
+    if ((threadIdx.x & 31) == 0) wb[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        Best b = wb[0];
+#pragma unroll
+        for (int w = 1; w < 8; w++) b = better(b, wb[w]);
+        part_v[blockIdx.x] = b.v;
+        part_i[blockIdx.x] = b.i;
+    }
+}
+
+/* Final stage: one CTA over n partials. An index of 0x7fffffff (no candidate
+ * beat -FLT_MAX) is reported as 0, like the reference's initial value. */
+__global__ void __launch_bounds__(1024)
+argmax_reduce_kernel(const float* part_v, const int* part_i, int n, int* out_token, float* out_value) {
+    __shared__ Best wb[32];
+    Best best{-FLT_MAX, 0x7fffffff};
+    for (int i = threadIdx.x; i < n; i += 1024) best = better(best, Best{part_v[i], part_i[i]});
+    best = warp_best(best);
+    if ((threadIdx.x & 31) == 0) wb[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        Best b = wb[threadIdx.x];
+        b = warp_best(b);
+        if (threadIdx.x == 0) {
+            *out_token = (b.i == 0x7fffffff) ? 0 : b.i;
+            if (out_value) *out_value = b.v;
+        }
+    }
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace vvb
+
+using namespace vvb;
+
+/* Upper bound on the number of CTAs (= argmax partials) a launch over V rows uses. */
+extern "C" int vvbk_lm_head_partials(int V) { return (V + kLmMinRowsPerCta - 1) / kLmMinRowsPerCta; }
+
+template <bool NORM>
+static int lm_head_resident_ctas(size_t smem) {
+    int dev = 0, sms = 148, per_sm = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lm_head_kernel<NORM>, kLmThreads, smem) != cudaSuccess ||
+        per_sm < 1)
+        per_sm = 1;
+    return sms * per_sm;
+}
+
+/* logits (may be NULL) and/or per-CTA argmax partials (part_v/part_i, may be
+ * NULL; at most vvbk_lm_head_partials(V) entries each, the number written
+ * comes back in *n_partials). norm_w != NULL: x is the
+ * hidden row and the final RMSNorm is applied first. Returns
+ * cudaErrorNotSupported when the fast form does not fit and partials or the
+ * norm were asked for (the scalar form only writes logits). */
+extern "C" int vvbk_lm_head(const void* x, const void* norm_w, float eps, const void* W, float* logits,
+                            float* part_v, int* part_i, int* n_partials, int V, int K, void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    if (n_partials) *n_partials = 0;
+    const bool fast = K % 8 == 0 && K <= 11264 &&   /* K floats of shared memory, under 48 KB with the statics */
+                      aligned16(x) && aligned16(W) && aligned16(norm_w);
+    if (!fast) {
+        if (part_v || norm_w || !logits) return (int)cudaErrorNotSupported;
+        lm_head_scalar_kernel<<<(V + 7) / 8, 256, 0, s>>>((const __half*)x, (const __half*)W, logits, V, K);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return (int)cudaGetLastError();
+    }
+    const size_t smem = (size_t)K * sizeof(float);
+    /* equal blocks of rows over the CTAs that are resident at once, never fewer than 32 rows each */
+    const int resident = norm_w ? lm_head_resident_ctas<true>(smem) : lm_head_resident_ctas<false>(smem);
+    int rows_per_cta = (V + resident - 1) / resident;
+    if (rows_per_cta < kLmMinRowsPerCta) rows_per_cta = kLmMinRowsPerCta;
+    rows_per_cta += rows_per_cta & 1;
+    const int grid = (V + rows_per_cta - 1) / rows_per_cta;
+    if (n_partials) *n_partials = grid;      /* entries of part_v / part_i this launch writes */
+    LmHeadArgs a{(const vec16*)x, (const vec16*)norm_w, (const vec16*)W, logits, part_v, part_i,
+                 V, K, K / 8, rows_per_cta, eps};
+    if (norm_w) lm_head_kernel<true><<<grid, kLmThreads, smem, s>>>(a);
+    else lm_head_kernel<false><<<grid, kLmThreads, smem, s>>>(a);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int vvbk_argmax_logits(const float* logits, int V, float* part_v, int* part_i, int nparts, void* stream) {
+    argmax_logits_kernel<<<nparts, 256, 0, (cudaStream_t)stream>>>(logits, V, part_v, part_i);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int vvbk_argmax_reduce(const float* part_v, const int* part_i, int n, int* out_token, float* out_value,
+                                  void* stream) {
+    argmax_reduce_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(part_v, part_i, n, out_token, out_value);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return (int)cudaGetLastError();
+}

@@ -68,6 +68,19 @@ int vvbk_act_quant(int mode, const void* a, const void* b, const void* weight, v
 /* acc[k] = max(acc[k], max_m |x[m,k]|), x FP16 [M,K], acc FP32 [K] (csrc/act_quant.cu). */
 int vvbk_col_absmax(const void* x, int M, int K, float* acc, void* stream);
 
+/* LM head (csrc/lm_head.cu). vvbk_lm_head: logits (may be NULL) and/or per-CTA
+ * argmax partials (may be NULL; at most vvbk_lm_head_partials(V) entries each,
+ * the number written is returned in *n_partials);
+ * norm_w != NULL applies the final RMSNorm to x first. Returns
+ * cudaErrorNotSupported (801) when K / alignment do not fit the fast form and
+ * anything but plain logits was asked for. */
+int vvbk_lm_head_partials(int V);
+int vvbk_lm_head(const void* x, const void* norm_w, float eps, const void* W, float* logits,
+                 float* part_v, int* part_i, int* n_partials, int V, int K, void* stream);
+int vvbk_argmax_logits(const float* logits, int V, float* part_v, int* part_i, int nparts, void* stream);
+int vvbk_argmax_reduce(const float* part_v, const int* part_i, int n, int* out_token, float* out_value,
+                       void* stream);
+
 /* Flat elementwise ops (csrc/elementwise.cu). */
 int vvbk_residual_add(void* x, const void* y, size_t n, void* stream);
 int vvbk_bias_add(void* out, const void* bias, int M, int N, void* stream);

@@ -258,6 +258,49 @@ vv_status_t vv_col_absmax_dev(const void* x, int M, int K, float* acc, void* str
     return from_cuda(vvbk_col_absmax(x, M, K, acc, stream));
 }
 
+/* -------------------------------------------------------------------- LM head */
+
+#define VVB_ARGMAX_PARTIALS 256   /* the reference's scratch size: src/cuda/lm_head.cu:171 */
+
+vv_status_t vv_lm_head_gemv_dev(const void* x, const void* W, void* logits, int V, int K, void* stream) {
+    if (!x || !W || !logits) return VV_ERR_NULL_PTR;
+    if (V < 0 || K < 0) return VV_ERR_INVALID_ARG;
+    if (V == 0) return VV_OK;
+    return from_cuda(vvbk_lm_head(x, NULL, 0.0f, W, (float*)logits, NULL, NULL, NULL, V, K, stream));
+}
+
+vv_status_t vv_argmax_dev(const void* logits, int V, void* scratch_v, void* scratch_i,
+                          void* out_token, void* out_value, void* stream) {
+    if (!logits || !scratch_v || !scratch_i || !out_token) return VV_ERR_NULL_PTR;
+    if (V <= 0) return VV_ERR_INVALID_ARG;
+    int err = vvbk_argmax_logits((const float*)logits, V, (float*)scratch_v, (int*)scratch_i,
+                                 VVB_ARGMAX_PARTIALS, stream);
+    if (err == 0)
+        err = vvbk_argmax_reduce((const float*)scratch_v, (const int*)scratch_i, VVB_ARGMAX_PARTIALS,
+                                 (int*)out_token, (float*)out_value, stream);
+    return from_cuda(err);
+}
+
+size_t vvb_lm_head_scratch_bytes(int V) {
+    return V > 0 ? (size_t)vvbk_lm_head_partials(V) * (sizeof(float) + sizeof(int)) : 0;
+}
+
+vv_status_t vvb_lm_head_argmax_dev(const void* x, const void* final_norm_w, float eps, const void* W,
+                                   int V, int K, void* logits, void* scratch, size_t scratch_bytes,
+                                   int32_t* out_token, float* out_value, void* stream) {
+    if (!x || !W || !scratch || !out_token) return VV_ERR_NULL_PTR;
+    if (V <= 0 || K <= 0) return VV_ERR_INVALID_ARG;
+    if (scratch_bytes < vvb_lm_head_scratch_bytes(V) || ((uintptr_t)scratch & 3u)) return VV_ERR_INVALID_ARG;
+    const int cap = vvbk_lm_head_partials(V);
+    float* part_v = (float*)scratch;
+    int* part_i = (int*)(part_v + cap);
+    int n = 0;
+    int err = vvbk_lm_head(x, final_norm_w, eps, W, (float*)logits, part_v, part_i, &n, V, K, stream);
+    if (err == 801) return VV_ERR_UNSUPPORTED;   /* cudaErrorNotSupported: K % 8, K > 11264 or alignment */
+    if (err == 0) err = vvbk_argmax_reduce(part_v, part_i, n, (int*)out_token, out_value, stream);
+    return from_cuda(err);
+}
+
 /* ------------------------------------------------------------ introspection */
 
 const char* vvb_version(void) { return "vvb200 " VVB_VERSION " sm_100a"; }

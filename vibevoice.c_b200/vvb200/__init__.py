@@ -75,6 +75,10 @@ SIGNATURES = {
     "vv_swiglu_q8_dev": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "vvb_add_rmsnorm_q8_dev": (_i, [_vp, _vp, _vp, _i, _i, _f, _i, _vp, _vp, _vp, _vp]),
     "vv_col_absmax_dev": (_i, [_vp, _i, _i, _vp, _vp]),
+    "vv_lm_head_gemv_dev": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
+    "vv_argmax_dev": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp]),
+    "vvb_lm_head_scratch_bytes": (_sz, [_i]),
+    "vvb_lm_head_argmax_dev": (_i, [_vp, _vp, _f, _vp, _i, _i, _vp, _vp, _sz, _vp, _vp, _vp]),
     "vvb_add_rmsnorm_dev": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
     "vvb_rope_qk_dev": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp]),
     "vvb_embedding_rmsnorm_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
@@ -194,6 +198,25 @@ def vv_swiglu_q8_dev(gate, up, M, K, layout, xq, sx, xsum, stream=None) -> int:
 def vvb_add_rmsnorm_q8_dev(hidden_inout, delta, weight, M, K, eps, layout, xq, sx, xsum, stream=None) -> int:
     return _lib.vvb_add_rmsnorm_q8_dev(_ptr(hidden_inout), _ptr(delta), _ptr(weight), M, K, eps, layout,
                                        _ptr(xq), _ptr(sx), _ptr(xsum), _stream(stream))
+
+
+def vv_lm_head_gemv_dev(x, W, logits, V, K, stream=None) -> int:
+    return _lib.vv_lm_head_gemv_dev(_ptr(x), _ptr(W), _ptr(logits), V, K, _stream(stream))
+
+
+def vv_argmax_dev(logits, V, scratch_v, scratch_i, out_token, out_value, stream=None) -> int:
+    return _lib.vv_argmax_dev(_ptr(logits), V, _ptr(scratch_v), _ptr(scratch_i), _ptr(out_token), _ptr(out_value),
+                              _stream(stream))
+
+
+def vvb_lm_head_scratch_bytes(V: int) -> int:
+    return int(_lib.vvb_lm_head_scratch_bytes(V))
+
+
+def vvb_lm_head_argmax_dev(x, final_norm_w, eps, W, V, K, logits, scratch, scratch_bytes, out_token, out_value,
+                           stream=None) -> int:
+    return _lib.vvb_lm_head_argmax_dev(_ptr(x), _ptr(final_norm_w), eps, _ptr(W), V, K, _ptr(logits), _ptr(scratch),
+                                       scratch_bytes, _ptr(out_token), _ptr(out_value), _stream(stream))
 
 
 def vv_col_absmax_dev(x, M, K, acc, stream=None) -> int:

@@ -135,6 +135,55 @@ def run(peak_gbs: float, peak_kind: str):
         "act_quant [14449,3584] natural", lambda: (rn(rows, H),) + qbufs(H),
         lambda b, s: ok(vv.vv_act_quant_dev(b[0], rows, H, 0, b[1], b[2], b[3], s)),
         rows * H * 2 + qout(H), rows * H * 2 + qout(H), peak_gbs))
+    # the decode tail: final RMSNorm + LM head [152064, 3584] + argmax (two launches), and the plain GEMV
+    V = 152064
+    head = torch.empty(V, H, device=dev, dtype=torch.float16).normal_(0, 0.02)
+    sbytes = vv.vvb_lm_head_scratch_bytes(V)
+    mk = lambda: (rn(H), torch.empty(sbytes, device=dev, dtype=torch.uint8), torch.empty(1, device=dev, dtype=torch.int32),
+                  torch.empty(V, device=dev, dtype=torch.float32))
+    out.append(_case(
+        "final_norm + lm_head + argmax [152064,3584]", mk,
+        lambda b, s: ok(vv.vvb_lm_head_argmax_dev(b[0], w, 1e-6, head, V, H, None, b[1], sbytes, b[2], None, s)),
+        V * H * 2, V * H * 2 + 2 * H * 2, peak_gbs, iters=10))
+    out.append(_case(
+        "lm_head_gemv [152064,3584] (logits)", mk,
+        lambda b, s: ok(vv.vv_lm_head_gemv_dev(b[0], head, b[3], V, H, s)),
+        V * H * 2, V * H * 2 + V * 4, peak_gbs, iters=10))
+    # one decode token (M = 1) of the 28-layer model, this library's kernels only (the GEMMs and the
+    # attention between them are the engine's): embedding, then per layer [norm (layer 0) or residual
+    # add + norm] -> bias + RoPE + KV append -> residual add + norm -> SwiGLU, then final norm + LM
+    # head + argmax; one CUDA graph, replayed. Launch-bound: reported as microseconds per token.
+    L, max_len = 28, 64
+    table = torch.empty(4096, H, device=dev, dtype=torch.float16).normal_(0, 0.02)
+    tok = torch.zeros(1, device=dev, dtype=torch.int32)
+    hid, dlt, nrm = rn(1, H), rn(1, H), rn(1, H)
+    q1, k1, v1, g1, u1 = rn(1, NQ, HD), rn(1, NKV, HD), rn(1, NKV, HD), rn(1, INTER), rn(1, INTER)
+    kc = [torch.zeros(max_len, NKV * HD, device=dev, dtype=torch.float16) for _ in range(L)]
+    vc = [torch.zeros(max_len, NKV * HD, device=dev, dtype=torch.float16) for _ in range(L)]
+    dpos = torch.tensor([7], device=dev, dtype=torch.int32)
+    scr = torch.empty(sbytes, device=dev, dtype=torch.uint8)
+
+    def decode_token(_i, s):
+        ok(vv.vvb_embedding_rmsnorm_dev(table, tok, hid, w, nrm, 1, H, 4096, 1e-6, s))
+        for layer in range(L):
+            if layer:
+                ok(vv.vvb_add_rmsnorm_dev(hid, dlt, w, nrm, 1, H, 1e-6, s))
+            ok(vv.vvb_rope_qk_append_dev(q1, k1, v1, bq, bk, bv, kc[layer], vc[layer], 1, NQ, NKV, HD, 0, 0, dpos,
+                                         1e6, 0, s))
+            ok(vv.vvb_add_rmsnorm_dev(hid, dlt, w, nrm, 1, H, 1e-6, s))
+            ok(vv.vvb_swiglu_dev(g1, u1, g1, INTER, s))
+        ok(vv.vvb_residual_add_dev(hid, dlt, H, s))
+        ok(vv.vvb_lm_head_argmax_dev(hid, w, 1e-6, head, V, H, None, scr, sbytes, tok, None, s))
+
+    launches0 = vv.launch_count()
+    decode_token(0, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    n_launch = vv.launch_count() - launches0
+    us_tok = _time_graph(decode_token, 1, 5)
+    out.append({"case": "decode step, 28 layers, M=1 (row kernels + LM head only)", "us": round(us_tok, 1),
+                "launches": n_launch})
+    del head
+    torch.cuda.empty_cache()
     return {"workload": "kernels", "peak_GB/s": peak_gbs, "peak_kind": "of " + peak_kind,
             "method": "CUDA-graph replay over rotating buffer sets > 2.5x L2, CUDA events, best of 3", "cases": out}
 
