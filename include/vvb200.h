@@ -233,6 +233,35 @@ vv_status_t vvb_lm_head_argmax_dev(const void* x, const void* final_norm_w, floa
                                    int V, int K, void* logits, void* scratch, size_t scratch_bytes,
                                    int32_t* out_token, float* out_value, void* stream);
 
+/** vvb_lm_head_argmax_dev without the scratch argument, for callers that
+ *  cannot allocate device memory. (No counterpart in the reference, whose
+ *  argmax takes caller scratch: include/vibevoice/device.h:710-713.)
+ *
+ *  Meant for a decode loop whose engine spent its device budget on one
+ *  workspace at load time and passes ops only their inputs and outputs, or for
+ *  a host application that calls this library from a callback without exposing
+ *  its allocator: such code cannot call cudaMalloc (the memory may be gone, and
+ *  the call stalls every stream of the device mid-token). The argmax partials
+ *  therefore live in a 64 KB array inside the library image, held by every GPU
+ *  that loads the library until the process exits.
+ *
+ *  Limit: V <= VVB_LM_HEAD_STATIC_MAX_V (VV_ERR_OVERFLOW beyond; use
+ *  vvb_lm_head_argmax_dev for taller heads). K, alignment and the meaning of
+ *  every other argument are those of vvb_lm_head_argmax_dev. The call makes no
+ *  cudaMalloc / cudaFree and no allocating library call.
+ *
+ *  The first call made while a given device is current looks up the array's
+ *  device address (cudaGetSymbolAddress) and caches it; make that first call
+ *  during start-up, before any stream capture. All calls on a device share the
+ *  array: it needs no clearing between calls (each launch overwrites what its
+ *  reduce step reads), but calls that overlap on the same GPU -- two streams or
+ *  two threads -- race on it; serialise them on one stream or give the others
+ *  their own scratch through vvb_lm_head_argmax_dev. */
+#define VVB_LM_HEAD_STATIC_MAX_V 262144
+vv_status_t vvb_lm_head_argmax_static_dev(const void* x, const void* final_norm_w, float eps,
+                                          const void* W, int V, int K, void* logits,
+                                          int32_t* out_token, float* out_value, void* stream);
+
 /** hidden_out[p] = table[clamp(ids[p], 0, vocab-1)] (bit copy) and
  *  normed_out[p] = rmsnorm(hidden_out[p]) in one kernel: the gather of
  *  src/inference/pipeline.c:2309 fused with layer 0's first norm

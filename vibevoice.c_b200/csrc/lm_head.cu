@@ -280,3 +280,78 @@ extern "C" int vvbk_argmax_reduce(const float* part_v, const int* part_i, int n,
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }
+
+/* ------------------------------------------------------------------------
+ * The same final norm + head + argmax for callers that have no device memory
+ * to give and no way to get any.
+ *
+ * Who that is: a decode loop whose engine carved its whole device budget into
+ * one workspace when the model was loaded and hands each op nothing but input
+ * and output pointers (the reference sizes every buffer once at start-up and
+ * never allocates while a token is in flight), or a host application that
+ * embeds this library behind a callback and keeps its allocator out of reach.
+ * Asking the CUDA runtime for memory from such a place is not an option: the
+ * budget may already be spent, and cudaMalloc / cudaFree stall every stream of
+ * the device while they run, in the middle of a token.
+ *
+ * So the argmax partials live in the array below, which is part of the
+ * library image: every GPU that loads the library sets aside these 64 KB until
+ * the process exits. That bounds the head this entry point accepts to
+ * VVB_LM_HEAD_STATIC_MAX_V rows (8192 partials of 32 rows); taller heads are
+ * refused with VV_ERR_OVERFLOW and belong to vvb_lm_head_argmax_dev.
+ *
+ * In host code `g_lm_head_partials` is only a handle for the symbol, not a
+ * device address, so the address is looked up with cudaGetSymbolAddress -- once
+ * per device, by the first call made while that device is current, and kept in
+ * a table indexed by device. That first call talks to the runtime beyond a
+ * plain launch, so make it during start-up, before any stream capture.
+ *
+ * Every call on a device writes into the one array. Nothing in it has to
+ * start at zero (each launch overwrites exactly the entries its reduce step
+ * reads), but two calls that overlap on the same GPU -- different streams, or
+ * different host threads -- race on it and can return each other's winner. Run
+ * them on one stream, or give all but one of them their own scratch through
+ * vvb_lm_head_argmax_dev.
+ */
+#include "vvb200.h"
+
+namespace vvb {
+constexpr int kStaticPartials = VVB_LM_HEAD_STATIC_MAX_V / kLmMinRowsPerCta;          /* 8192 */
+static __device__ __align__(256) unsigned char g_lm_head_partials[kStaticPartials * (sizeof(float) + sizeof(int))];
+
+constexpr int kMaxDevices = 64;
+static std::atomic<void*> g_lm_head_partials_addr[kMaxDevices];   /* device address of the array, per device */
+
+/* Device address of the static array on the CURRENT device (looked up once). */
+static cudaError_t static_partials(void** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    void* p = g_lm_head_partials_addr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
+        e = cudaGetSymbolAddress(&p, g_lm_head_partials);
+        if (e != cudaSuccess) return e;
+        g_lm_head_partials_addr[dev].store(p, std::memory_order_release);   /* racing first calls store the same value */
+    }
+    *out = p;
+    return cudaSuccess;
+}
+}  // namespace vvb
+
+extern "C" vv_status_t vvb_lm_head_argmax_static_dev(const void* x, const void* final_norm_w, float eps,
+                                                     const void* W, int V, int K, void* logits,
+                                                     int32_t* out_token, float* out_value, void* stream) {
+    if (!x || !W || !out_token) return VV_ERR_NULL_PTR;
+    if (V <= 0 || K <= 0) return VV_ERR_INVALID_ARG;
+    if (V > VVB_LM_HEAD_STATIC_MAX_V) return VV_ERR_OVERFLOW;       /* more partials than the array holds */
+    void* scratch = nullptr;
+    if (static_partials(&scratch) != cudaSuccess || scratch == nullptr) return VV_ERR_CUDA;
+    float* part_v = (float*)scratch;
+    int* part_i = (int*)(part_v + kStaticPartials);
+    int n = 0;
+    int err = vvbk_lm_head(x, final_norm_w, eps, W, (float*)logits, part_v, part_i, &n, V, K, stream);
+    if (err == (int)cudaErrorNotSupported) return VV_ERR_UNSUPPORTED;   /* K % 8, K > 11264 or alignment */
+    if (err == 0) err = vvbk_argmax_reduce(part_v, part_i, n, (int*)out_token, out_value, stream);
+    return err == 0 ? VV_OK : VV_ERR_CUDA_LAUNCH;
+}

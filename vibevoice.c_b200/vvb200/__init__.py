@@ -79,6 +79,7 @@ SIGNATURES = {
     "vv_argmax_dev": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "vvb_lm_head_scratch_bytes": (_sz, [_i]),
     "vvb_lm_head_argmax_dev": (_i, [_vp, _vp, _f, _vp, _i, _i, _vp, _vp, _sz, _vp, _vp, _vp]),
+    "vvb_lm_head_argmax_static_dev": (_i, [_vp, _vp, _f, _vp, _i, _i, _vp, _vp, _vp, _vp]),
     "vvb_add_rmsnorm_dev": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
     "vvb_rope_qk_dev": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp]),
     "vvb_embedding_rmsnorm_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
@@ -217,6 +218,17 @@ def vvb_lm_head_argmax_dev(x, final_norm_w, eps, W, V, K, logits, scratch, scrat
                            stream=None) -> int:
     return _lib.vvb_lm_head_argmax_dev(_ptr(x), _ptr(final_norm_w), eps, _ptr(W), V, K, _ptr(logits), _ptr(scratch),
                                        scratch_bytes, _ptr(out_token), _ptr(out_value), _stream(stream))
+
+
+VVB_LM_HEAD_STATIC_MAX_V = 262144
+
+
+def vvb_lm_head_argmax_static_dev(x, final_norm_w, eps, W, V, K, logits, out_token, out_value, stream=None) -> int:
+    """The fused head + argmax with its scratch inside the library (no device
+    memory from the caller, none allocated); V <= VVB_LM_HEAD_STATIC_MAX_V.
+    Calls on one GPU must not overlap: they share that scratch."""
+    return _lib.vvb_lm_head_argmax_static_dev(_ptr(x), _ptr(final_norm_w), eps, _ptr(W), V, K, _ptr(logits),
+                                              _ptr(out_token), _ptr(out_value), _stream(stream))
 
 
 def vv_col_absmax_dev(x, M, K, acc, stream=None) -> int:
