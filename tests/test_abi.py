@@ -64,7 +64,8 @@ def test_declarations_agree_with_the_reference_headers(tmp_path):
     reference's prototype and links against the static archive."""
     names = ["vv_embedding_dev", "vv_rmsnorm_dev", "vv_rope_dev", "vv_swiglu_dev", "vv_swiglu_fused_dev",
              "vv_residual_add_dev", "vv_bias_add_dev", "vv_fp32_to_fp16_dev", "vv_fp16_to_fp32_dev",
-             "vv_act_quant_dev", "vv_rmsnorm_q8_dev", "vv_swiglu_q8_dev", "vv_col_absmax_dev"]
+             "vv_act_quant_dev", "vv_rmsnorm_q8_dev", "vv_swiglu_q8_dev", "vv_col_absmax_dev",
+             "vv_lm_head_gemv_dev", "vv_argmax_dev"]
     src = tmp_path / "both.c"
     src.write_text('#include "vibevoice/device.h"\n#include "vvb200.h"\n#include <stdio.h>\n'
                    "int main(void) {\n  const void* fns[] = {" + ", ".join(f"(const void*){n}" for n in names) +
