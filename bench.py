@@ -454,6 +454,9 @@ def main():
     ap.add_argument("--workload", choices=["chain", "kernels"], default="chain",
                     help="chain: the benchmark line (config 5); kernels: one line of per-kernel timings at the "
                          "shapes of configs 1-4 and for the int8 activation quantizers (1 GPU)")
+    ap.add_argument("--case", default=None, help="--workload kernels: run only the cases whose name contains this")
+    ap.add_argument("--plain-launches", action="store_true",
+                    help="--workload kernels: four direct launches per case, no graphs, no timing (profiler captures)")
     ap.add_argument("--cpu-baseline-worker", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
 
@@ -471,7 +474,7 @@ def main():
         assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
         torch.cuda.set_device(0)
         from vvb200 import kernel_bench
-        return kernel_bench.main(*measured_hbm_peak())
+        return kernel_bench.main(*measured_hbm_peak(), only=args.case, plain=args.plain_launches)
     return run_native(args)
 
 

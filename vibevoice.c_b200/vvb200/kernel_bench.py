@@ -48,7 +48,21 @@ def _nsets(bytes_per_set):
     return max(1, min(48, int(2.5 * L2_BYTES / bytes_per_set) + 1))
 
 
+ONLY = None      # substring filter on case names (bench.py --case), for profiler runs
+PLAIN = False    # direct launches, few of them, instead of graph replays (bench.py --plain-launches)
+
+
 def _case(name, make_set, call, set_bytes, algo_bytes, peak, iters=40):
+    if ONLY is not None and ONLY not in name:
+        return None
+    if PLAIN:
+        # a handful of direct launches over two buffer sets: what a profiler capture wants
+        sets = [make_set() for _ in range(2)]
+        s = torch.cuda.current_stream()
+        for i in range(4):
+            call(sets[i % 2], s)
+        torch.cuda.synchronize()
+        return {"case": name, "plain_launches": 4}
     ns = _nsets(set_bytes)
     sets = [make_set() for _ in range(ns)]
     cold = _time_graph(lambda i, s: call(sets[i], s), ns, iters)
@@ -175,18 +189,22 @@ def run(peak_gbs: float, peak_kind: str):
         ok(vv.vvb_residual_add_dev(hid, dlt, H, s))
         ok(vv.vvb_lm_head_argmax_dev(hid, w, 1e-6, head, V, H, None, scr, sbytes, tok, None, s))
 
-    launches0 = vv.launch_count()
-    decode_token(0, torch.cuda.current_stream())
-    torch.cuda.synchronize()
-    n_launch = vv.launch_count() - launches0
-    us_tok = _time_graph(decode_token, 1, 5)
-    out.append({"case": "decode step, 28 layers, M=1 (row kernels + LM head only)", "us": round(us_tok, 1),
-                "launches": n_launch})
+    if not PLAIN and (ONLY is None or ONLY in "decode step"):
+        launches0 = vv.launch_count()
+        decode_token(0, torch.cuda.current_stream())
+        torch.cuda.synchronize()
+        n_launch = vv.launch_count() - launches0
+        us_tok = _time_graph(decode_token, 1, 5)
+        out.append({"case": "decode step, 28 layers, M=1 (row kernels + LM head only)", "us": round(us_tok, 1),
+                    "launches": n_launch})
     del head
     torch.cuda.empty_cache()
     return {"workload": "kernels", "peak_GB/s": peak_gbs, "peak_kind": "of " + peak_kind,
-            "method": "CUDA-graph replay over rotating buffer sets > 2.5x L2, CUDA events, best of 3", "cases": out}
+            "method": "CUDA-graph replay over rotating buffer sets > 2.5x L2, CUDA events, best of 3",
+            "cases": [c for c in out if c is not None]}
 
 
-def main(peak_gbs, peak_kind):
+def main(peak_gbs, peak_kind, only=None, plain=False):
+    global ONLY, PLAIN
+    ONLY, PLAIN = only, plain
     print(json.dumps(run(peak_gbs, peak_kind)), flush=True)
