@@ -1,0 +1,208 @@
+"""The incumbent on the same GPU: the reference's own CUDA kernels for this
+path (src/cuda/rmsnorm.cu, rope.cu, swiglu.cu, embedding.cu, conv_vae.cu,
+act_quant.cu, lm_head.cu), compiled unmodified with its release flags into
+oracle/_ref/libvvref_cuda.so by `make -C oracle`, timed beside this library's
+kernels under one protocol (CUDA-graph replay, buffers rotating over more than
+2.5x the L2, CUDA events, best of three), and scored against the CPU oracle.
+
+Skipped where that library is absent. Timings are written to
+gpurun_out/incumbent.json when that directory exists; the assertions only
+demand that the new kernels are not slower.
+"""
+import ctypes as C
+import json
+import os
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_CUDA = os.path.join(ROOT, "oracle", "_ref", "libvvref_cuda.so")
+H, NQ, NKV, HD, INTER = 3584, 28, 4, 128, 18944
+RESULTS = {}
+
+
+@pytest.fixture(scope="module")
+def libs():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    if not os.path.exists(REF_CUDA):
+        pytest.skip("the reference's CUDA kernels were not compiled (oracle/_ref/libvvref_cuda.so)")
+    import vvb200
+    torch.cuda.set_device(0)
+    ref = C.CDLL(REF_CUDA)
+    vp, i, f = C.c_void_p, C.c_int, C.c_float
+    ref.vv_rmsnorm_dev.argtypes = [vp, vp, vp, i, i, f, vp]
+    ref.vv_residual_add_dev.argtypes = [vp, vp, i, vp]
+    ref.vv_rope_dev.argtypes = [vp, i, i, i, i, vp, f, vp]
+    ref.vv_swiglu_dev.argtypes = [vp, vp, vp, i, vp]
+    ref.vv_embedding_dev.argtypes = [vp, vp, vp, i, i, vp]
+    ref.vv_rmsnorm_q8_dev.argtypes = [vp, vp, i, i, f, i, vp, vp, vp, vp]
+    ref.vv_swiglu_q8_dev.argtypes = [vp, vp, i, i, i, vp, vp, vp, vp]
+    ref.vv_lm_head_gemv_dev.argtypes = [vp, vp, vp, i, i, vp]
+    ref.vv_argmax_dev.argtypes = [vp, i, vp, vp, vp, vp, vp]
+    return vvb200, ref
+
+
+def time_graph(fn, nsets, iters=20):
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for k in range(min(3, nsets)):
+            fn(k % nsets, s.cuda_stream)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for k in range(iters):
+                fn(k % nsets, s.cuda_stream)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = 1e30
+        for _ in range(3):
+            e0.record(s)
+            g.replay()
+            e1.record(s)
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) * 1e3 / iters)
+    return best
+
+
+def nsets(nbytes):
+    return max(1, min(24, int(2.5 * 126e6 / nbytes) + 1))
+
+
+def p(t):
+    return t.data_ptr()
+
+
+def record(name, ours_us, ref_us, extra=None):
+    RESULTS[name] = {"ours_us": round(ours_us, 2), "reference_cuda_us": round(ref_us, 2),
+                     "speedup": round(ref_us / ours_us, 2), **(extra or {})}
+    print(name, RESULTS[name])
+    out = os.path.join(ROOT, "gpurun_out")
+    if os.path.isdir(out):
+        with open(os.path.join(out, "incumbent.json"), "w") as fh:
+            json.dump(RESULTS, fh, indent=1)
+
+
+def rn(*s):
+    return torch.randn(*s, device="cuda").half()
+
+
+@pytest.mark.parametrize("rows", [4096, 14449])
+def test_add_rmsnorm_vs_incumbent(libs, rows):
+    vv, ref = libs
+    n = nsets(rows * H * 6)
+    hs, ds, os_ = [rn(rows, H) for _ in range(n)], [rn(rows, H) for _ in range(n)], [rn(rows, H) for _ in range(n)]
+    w = torch.ones(H, device="cuda").half()
+    ours = time_graph(lambda k, s: vv.vvb_add_rmsnorm_dev(p(hs[k]), p(ds[k]), p(w), p(os_[k]), rows, H, 1e-6, s), n)
+
+    def ref_pair(k, s):
+        assert ref.vv_residual_add_dev(p(hs[k]), p(ds[k]), rows * H, s) == 0
+        assert ref.vv_rmsnorm_dev(p(hs[k]), p(w), p(os_[k]), rows, H, 1e-6, s) == 0
+    theirs = time_graph(ref_pair, n)
+    record(f"residual_add + rmsnorm [{rows},3584]", ours, theirs)
+    assert ours < theirs
+
+
+@pytest.mark.parametrize("rows", [4096, 14449])
+def test_rope_vs_incumbent(libs, orc, rows):
+    vv, ref = libs
+    n = nsets(rows * (NQ + NKV) * HD * 2)
+    qs, ks = [rn(rows, NQ, HD) for _ in range(n)], [rn(rows, NKV, HD) for _ in range(n)]
+    ours = time_graph(lambda k, s: vv.vvb_rope_qk_dev(p(qs[k]), p(ks[k]), rows, NQ, NKV, HD, 0, None, 1e6, s), n)
+
+    def ref_pair(k, s):
+        assert ref.vv_rope_dev(p(qs[k]), rows, NQ, HD, 0, None, 1e6, s) == 0
+        assert ref.vv_rope_dev(p(ks[k]), rows, NKV, HD, 0, None, 1e6, s) == 0
+    theirs = time_graph(ref_pair, n)
+    # accuracy at the tail of the prompt, against the CPU oracle (the reference's CUDA build is fast-math)
+    x = np.random.default_rng(0).standard_normal((64, NKV, HD)).astype(np.float16)
+    pos = rows - 64
+    want = orc.rope_f16(x, pos, 1e6)
+    a, b = torch.from_numpy(x).cuda(), torch.from_numpy(x).cuda()
+    assert vv.vv_rope_dev(p(a), 64, NKV, HD, pos, None, 1e6, 0) == 0
+    assert ref.vv_rope_dev(p(b), 64, NKV, HD, pos, None, 1e6, None) == 0
+    torch.cuda.synchronize()
+    e_ours = float(orc.rope_error_in_ulps(a.cpu().numpy(), want, x).max())
+    e_ref = float(orc.rope_error_in_ulps(b.cpu().numpy(), want, x).max())
+    record(f"rope Q+K [{rows},32,128]", ours, theirs,
+           {"max_err_fp16_ulp_ours": round(e_ours, 2), "max_err_fp16_ulp_reference_cuda": round(e_ref, 2)})
+    assert ours < theirs and e_ours <= 2.0
+
+
+@pytest.mark.parametrize("rows", [64, 4096, 14449])
+def test_swiglu_vs_incumbent(libs, rows):
+    vv, ref = libs
+    n = nsets(rows * INTER * 4)
+    gs, us = [rn(rows, INTER) for _ in range(n)], [rn(rows, INTER) for _ in range(n)]
+    ours = time_graph(lambda k, s: vv.vv_swiglu_dev(p(gs[k]), p(us[k]), p(gs[k]), rows * INTER, s), n)
+    theirs = time_graph(lambda k, s: ref.vv_swiglu_dev(p(gs[k]), p(us[k]), p(gs[k]), rows * INTER, s), n)
+    record(f"swiglu [{rows},18944]", ours, theirs)
+    assert ours < theirs
+
+
+def test_embedding_vs_incumbent(libs):
+    vv, ref = libs
+    V, rows = 151936, 16384
+    table = torch.empty(V, H, device="cuda", dtype=torch.float16).normal_(0, 0.02)
+    n = 3
+    ids = [torch.randint(0, V, (rows,), device="cuda", dtype=torch.int32) for _ in range(n)]
+    outs = [torch.empty(rows, H, device="cuda", dtype=torch.float16) for _ in range(n)]
+    nrm = [torch.empty(rows, H, device="cuda", dtype=torch.float16) for _ in range(n)]
+    w = torch.ones(H, device="cuda").half()
+    ours = time_graph(lambda k, s: vv.vvb_embedding_rmsnorm_dev(p(table), p(ids[k]), p(outs[k]), p(w), p(nrm[k]), rows, H,
+                                                               V, 1e-6, s), n)
+
+    def ref_pair(k, s):
+        assert ref.vv_embedding_dev(p(table), p(ids[k]), p(outs[k]), rows, H, s) == 0
+        assert ref.vv_rmsnorm_dev(p(outs[k]), p(w), p(nrm[k]), rows, H, 1e-6, s) == 0
+    theirs = time_graph(ref_pair, n)
+    record("embedding gather + rmsnorm, 16384 of [151936,3584]", ours, theirs)
+    assert ours < theirs
+
+
+def test_q8_vs_incumbent(libs):
+    vv, ref = libs
+    rows = 4096
+    w = torch.ones(H, device="cuda").half()
+    for K, kind in ((H, "rmsnorm_q8"), (INTER, "swiglu_q8")):
+        n = nsets(rows * K * 3)
+        xs, us = [rn(rows, K) for _ in range(n)], [rn(rows, K) for _ in range(n)]
+        q = [torch.empty(rows, K, device="cuda", dtype=torch.int8) for _ in range(n)]
+        sx = torch.empty(rows, device="cuda")
+        xsum = torch.empty(rows, K // 32, device="cuda", dtype=torch.int32)
+        if kind == "rmsnorm_q8":
+            ours = time_graph(lambda k, s: vv.vv_rmsnorm_q8_dev(p(xs[k]), p(w), rows, K, 1e-6, 0, p(q[k]), p(sx), p(xsum), s), n)
+            theirs = time_graph(lambda k, s: ref.vv_rmsnorm_q8_dev(p(xs[k]), p(w), rows, K, 1e-6, 0, p(q[k]), p(sx), p(xsum), s), n)
+        else:
+            ours = time_graph(lambda k, s: vv.vv_swiglu_q8_dev(p(xs[k]), p(us[k]), rows, K, 0, p(q[k]), p(sx), p(xsum), s), n)
+            theirs = time_graph(lambda k, s: ref.vv_swiglu_q8_dev(p(xs[k]), p(us[k]), rows, K, 0, p(q[k]), p(sx), p(xsum), s), n)
+        record(f"{kind} [{rows},{K}]", ours, theirs)
+        assert ours < theirs
+
+
+def test_lm_head_vs_incumbent(libs):
+    vv, ref = libs
+    V = 152064
+    W = torch.empty(V, H, device="cuda", dtype=torch.float16).normal_(0, 0.02)
+    x, w = rn(H), torch.ones(H, device="cuda").half()
+    nx = torch.empty(H, device="cuda", dtype=torch.float16)
+    logits = torch.empty(V, device="cuda", dtype=torch.float32)
+    sv, si = torch.empty(256, device="cuda"), torch.empty(256, device="cuda", dtype=torch.int32)
+    tok = torch.zeros(1, device="cuda", dtype=torch.int32)
+    nb = vv.vvb_lm_head_scratch_bytes(V)
+    scratch = torch.empty(nb, device="cuda", dtype=torch.uint8)
+    ours = time_graph(lambda k, s: vv.vvb_lm_head_argmax_dev(p(x), p(w), 1e-6, p(W), V, H, None, p(scratch), nb, p(tok), None, s), 1, 10)
+    t_ours = int(tok.item())
+
+    def ref_chain(k, s):
+        assert ref.vv_rmsnorm_dev(p(x), p(w), p(nx), 1, H, 1e-6, s) == 0
+        assert ref.vv_lm_head_gemv_dev(p(nx), p(W), p(logits), V, H, s) == 0
+        assert ref.vv_argmax_dev(p(logits), V, p(sv), p(si), p(tok), None, s) == 0
+    theirs = time_graph(ref_chain, 1, 10)
+    record("final norm + lm_head + argmax [152064,3584]", ours, theirs, {"same_token": t_ours == int(tok.item())})
+    assert ours < theirs
