@@ -448,6 +448,43 @@ def test_empty_work_and_errors(vv):
     assert vv.vv_rope_dev(x, 1, 1, 1026, 0, None, 1e4) == vv.VV_ERR_UNSUPPORTED
 
 
+def test_sizes_beyond_int32(vv, orc):
+    """Element counts and table offsets past 2^31: the reference's kernels index
+    with `int` (src/cuda/swiglu.cu:79, embedding.cu:34-35); these take size_t."""
+    n = (1 << 31) + 8 * 1000 + 3                      # > INT_MAX elements, not a multiple of 8
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    gate = torch.randn(n, generator=gen, device="cuda", dtype=torch.float16)
+    up = torch.randn(n, generator=gen, device="cuda", dtype=torch.float16)
+    spots = [0, 12345, (1 << 31) - 5, (1 << 31) + 1, n - 4100, n - 11]      # windows checked against the oracle
+    want = {s: orc.swiglu_f16(host(gate[s:s + 11]), host(up[s:s + 11])) for s in spots}
+    assert vv.vvb_swiglu_dev(gate, up, gate, n) == 0
+    for s in spots:
+        assert orc.ulp_distance(host(gate[s:s + 11]), want[s]).max() <= SWIGLU_ULP
+    y = torch.ones(n, device="cuda", dtype=torch.float16)
+    before = {s: host(gate[s:s + 11]).astype(np.float32) for s in spots}
+    assert vv.vvb_residual_add_dev(gate, y, n) == 0
+    for s in spots:
+        assert np.array_equal(host(gate[s:s + 11]), (before[s] + 1).astype(np.float16))
+    del gate, up, y
+    torch.cuda.empty_cache()
+    # a table whose last rows start beyond 2^31 elements
+    V, H = 700_000, 3584
+    table = torch.empty(V, H, device="cuda", dtype=torch.float16)
+    ids = torch.tensor([V - 1, 0, 650_123, 599_187, V - 1], dtype=torch.int32)
+    for r in set(ids.tolist()):
+        table[r] = torch.randn(H, generator=gen, device="cuda", dtype=torch.float16)
+    out = torch.empty(ids.numel(), H, device="cuda", dtype=torch.float16)
+    nrm = torch.empty_like(out)
+    w = torch.ones(H, device="cuda", dtype=torch.float16)
+    assert vv.vv_embedding_dev(table, ids.cuda(), out, ids.numel(), H) == 0
+    assert torch.equal(out.view(torch.int16), table[ids.cuda().long()].view(torch.int16))
+    out.zero_()
+    assert vv.vvb_embedding_rmsnorm_dev(table, ids.cuda(), out, w, nrm, ids.numel(), H, V, 1e-6) == 0
+    assert torch.equal(out.view(torch.int16), table[ids.cuda().long()].view(torch.int16))
+    _, want_n = orc.add_rmsnorm_f16(host(out), None, host(w), 1e-6)
+    assert orc.ulp_distance(host(nrm), want_n).max() <= NORM_ULP
+
+
 # --------------------------------------------------------------- full-size properties
 def test_full_size_properties(vv, orc):
     """At the full BASELINE sizes the oracle checks a sample of rows and the
