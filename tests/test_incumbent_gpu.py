@@ -5,9 +5,9 @@ oracle/_ref/libvvref_cuda.so by `make -C oracle`, timed beside this library's
 kernels under one protocol (CUDA-graph replay, buffers rotating over more than
 2.5x the L2, CUDA events, best of three), and scored against the CPU oracle.
 
-Skipped where that library is absent. Timings are written to
-gpurun_out/incumbent.json when that directory exists; the assertions only
-demand that the new kernels are not slower.
+Skipped where that library is absent. Timings are also written to
+incumbent.json in the run's output directory when there is one; the assertions
+only demand that the new kernels are not slower.
 """
 import ctypes as C
 import json
