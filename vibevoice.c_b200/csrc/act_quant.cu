@@ -105,12 +105,11 @@ act_quant_kernel(const ActQuantArgs a) {
      * per-run sum needs. */
     int8_t* xq = a.xq + (size_t)row * (size_t)a.nvec * 8u;
     int32_t* xsum = a.xsum ? a.xsum + (size_t)row * (size_t)(a.nvec >> 2) : nullptr;
+    const float2 inv2 = splat2(inv);
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
         const int v = t + j * G;
         const bool ok = v < a.nvec;
-        float f[8];
-        unpack8(yv[j], f);
         /* round-half-even without the conversion unit: p = v*inv is rounded
          * to float first (as the CPU does) and adding 1.5*2^23 rounds it to an
          * integer in the float adder's nearest-even mode; the low byte of the
@@ -120,9 +119,17 @@ act_quant_kernel(const ActQuantArgs a) {
          * 127.00002 and rounds to at most 127. (Rows holding an infinity or
          * a NaN have no defined quantization on the CPU path either.) */
         uint32_t rb[8];
+        const uint32_t* yw = reinterpret_cast<const uint32_t*>(&yv[j]);
 #pragma unroll
-        for (int e = 0; e < 8; e++)
-            rb[e] = __float_as_uint(__fadd_rn(__fmul_rn(f[e], inv), 12582912.0f));
+        for (int e = 0; e < 4; e++) {
+            /* two columns per packed multiply; the adds stay scalar: the
+             * assembler merges a packed multiply and a packed add into one
+             * fused multiply-add even when both name .rn, which skips the
+             * rounding of the product and moves ties */
+            const float2 p = mul2(unpack2(yw[e]), inv2);
+            rb[2 * e] = __float_as_uint(__fadd_rn(p.x, 12582912.0f));
+            rb[2 * e + 1] = __float_as_uint(__fadd_rn(p.y, 12582912.0f));
+        }
         const uint32_t lo = __byte_perm(__byte_perm(rb[0], rb[1], 0x0040), __byte_perm(rb[2], rb[3], 0x0040), 0x5410);
         const uint32_t hi = __byte_perm(__byte_perm(rb[4], rb[5], 0x0040), __byte_perm(rb[6], rb[7], 0x0040), 0x5410);
         int s = __dp4a((int)lo, 0x01010101, __dp4a((int)hi, 0x01010101, 0));   /* sum of the 8 signed bytes */

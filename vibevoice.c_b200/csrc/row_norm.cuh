@@ -29,12 +29,13 @@ __device__ __forceinline__ float inv_rms(double ss, int hidden, float eps) {
 }
 
 __device__ __forceinline__ vec16 scale_row_vec(const vec16& h, const vec16& w, float inv) {
-    float f[8], g[8];
-    unpack8(h, f);
-    unpack8(w, g);
-#pragma unroll
-    for (int e = 0; e < 8; e++) f[e] = __fmul_rn(__fmul_rn(f[e], inv), g[e]);
-    return pack8(f);
+    const float2 i2 = splat2(inv);
+    vec16 r;
+    r.x = pack2(mul2(mul2(unpack2(h.x), i2), unpack2(w.x)));
+    r.y = pack2(mul2(mul2(unpack2(h.y), i2), unpack2(w.y)));
+    r.z = pack2(mul2(mul2(unpack2(h.z), i2), unpack2(w.z)));
+    r.w = pack2(mul2(mul2(unpack2(h.w), i2), unpack2(w.w)));
+    return r;
 }
 
 /* ------------------------------------------------------------ one row, one group
@@ -85,18 +86,18 @@ __device__ __forceinline__ void row_norm_produce(const RowNormArgs& a, int row, 
     double ss = 0.0;
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
-        float f[8];
-        unpack8(hv[j], f);
-        if (has_delta) {
-            float d[8];
-            unpack8(dv[j], d);
+        uint32_t* hw = reinterpret_cast<uint32_t*>(&hv[j]);
+        const uint32_t* dw = reinterpret_cast<const uint32_t*>(&dv[j]);
 #pragma unroll
-            for (int e = 0; e < 8; e++) f[e] = __fadd_rn(f[e], d[e]);
-            hv[j] = pack8(f);       /* round to FP16: this is the new hidden state */
-            unpack8(hv[j], f);      /* and the norm sees the rounded values */
+        for (int e = 0; e < 4; e++) {
+            float2 f = unpack2(hw[e]);
+            if (has_delta) {
+                hw[e] = pack2(add2(f, unpack2(dw[e])));   /* round to FP16: this is the new hidden state */
+                f = unpack2(hw[e]);                        /* and the norm sees the rounded values */
+            }
+            ss = fma((double)f.x, (double)f.x, ss);
+            ss = fma((double)f.y, (double)f.y, ss);
         }
-#pragma unroll
-        for (int e = 0; e < 8; e++) ss = fma((double)f[e], (double)f[e], ss);
     }
     if (a.row_out != nullptr) {
         vec16* rp = a.row_out + roff;

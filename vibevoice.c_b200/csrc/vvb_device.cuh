@@ -30,6 +30,37 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+__device__ __forceinline__ uint32_t pack2(float2 a) { return pack2(a.x, a.y); }
+
+/* Packed FP32 pairs: sm_100 issues one instruction for two lanes, each
+ * rounded to nearest even exactly as the scalar operation is, so results do
+ * not change; the kernels that are bound by instruction issue use these.
+ * HAZARD: never feed a mul2 result into an add2. The toolchain (CUDA 12.9)
+ * merges a packed product and a packed sum into one fused multiply-add,
+ * with the __fmul2_rn / __fadd2_rn intrinsics and with PTX that names .rn
+ * alike, which skips the rounding of the product (observed: ties of the int8
+ * quantizer rounded the wrong way). Products of products and lone sums are
+ * safe; a product that is summed keeps its add scalar. */
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 r;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "mul.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return r;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 r;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(r.x), "=f"(r.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return r;
+}
+__device__ __forceinline__ float2 splat2(float a) { return make_float2(a, a); }
+
 __device__ __forceinline__ void unpack8(const vec16& v, float (&f)[8]) {
     float2 t;
     t = unpack2(v.x); f[0] = t.x; f[1] = t.y;
