@@ -55,6 +55,8 @@ __device__ __forceinline__ int q8_pos(int layout, int j) {
 template <int VPT, int MODE>
 __global__ void __launch_bounds__(1024)
 act_quant_kernel(const ActQuantArgs a) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ float red_max[32];
     const int t = threadIdx.x, G = blockDim.x;
     const int row = blockIdx.x;
@@ -170,6 +172,8 @@ constexpr int kColRows = 32;
 
 __global__ void __launch_bounds__(kColThreads)
 col_absmax_kernel(const vec16* __restrict__ x, int M, int nvec, float* __restrict__ acc) {
+    pdl_wait();
+    pdl_trigger();
     const int v = blockIdx.x * kColThreads + threadIdx.x;
     if (v >= nvec) return;
     const int m0 = blockIdx.y * kColRows;
@@ -205,6 +209,8 @@ col_absmax_kernel(const vec16* __restrict__ x, int M, int nvec, float* __restric
 
 __global__ void __launch_bounds__(256)
 col_absmax_scalar_kernel(const __half* __restrict__ x, int M, int K, float* __restrict__ acc) {
+    pdl_wait();
+    pdl_trigger();
     const int k = blockIdx.x * 256 + threadIdx.x;
     if (k >= K) return;
     const int m0 = blockIdx.y * 64;
@@ -221,9 +227,9 @@ static cudaError_t launch_q(const ActQuantArgs& a, cudaStream_t s) {
     int vpt = (a.nvec + threads - 1) / threads;
     if (vpt == 3) vpt = 4;
     switch (vpt) {
-        case 1: act_quant_kernel<1, MODE><<<a.rows, threads, 0, s>>>(a); break;
-        case 2: act_quant_kernel<2, MODE><<<a.rows, threads, 0, s>>>(a); break;
-        case 4: act_quant_kernel<4, MODE><<<a.rows, threads, 0, s>>>(a); break;
+        case 1: launch_pdl(act_quant_kernel<1, MODE>, dim3(a.rows), dim3(threads), 0, s, a); break;
+        case 2: launch_pdl(act_quant_kernel<2, MODE>, dim3(a.rows), dim3(threads), 0, s, a); break;
+        case 4: launch_pdl(act_quant_kernel<4, MODE>, dim3(a.rows), dim3(threads), 0, s, a); break;
         default: return cudaErrorInvalidValue;
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -264,11 +270,11 @@ extern "C" int vvbk_col_absmax(const void* x, int M, int K, float* acc, void* st
         const dim3 grid((unsigned)((nvec + kColThreads - 1) / kColThreads),
                         (unsigned)((M + kColRows - 1) / kColRows));
         if (grid.y > 65535u) return (int)cudaErrorInvalidValue;
-        col_absmax_kernel<<<grid, kColThreads, 0, s>>>((const vec16*)x, M, nvec, acc);
+        launch_pdl(col_absmax_kernel, grid, dim3(kColThreads), 0, s, (const vec16*)x, M, nvec, acc);
     } else {
         const dim3 grid((unsigned)((K + 255) / 256), (unsigned)((M + 63) / 64));
         if (grid.y > 65535u) return (int)cudaErrorInvalidValue;
-        col_absmax_scalar_kernel<<<grid, 256, 0, s>>>((const __half*)x, M, K, acc);
+        launch_pdl(col_absmax_scalar_kernel, grid, dim3(256), 0, s, (const __half*)x, M, K, acc);
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();

@@ -43,6 +43,8 @@ struct ChainArgs {
 
 __global__ void __launch_bounds__(kChainThreads, 4)
 layer_chain_kernel(const __grid_constant__ ChainArgs a) {
+    pdl_wait();
+    pdl_trigger();
     unsigned b = blockIdx.x;
     const int t = threadIdx.x;
     if (b < a.norm_ctas) {
@@ -102,7 +104,7 @@ extern "C" int vvbk_layer_chain(void* hidden, const void* delta, const void* wei
     const size_t swiglu_ctas = (a.swiglu_vecs + per_cta - 1) / per_cta;
     const size_t total = (size_t)a.norm_ctas + a.rope_ctas + swiglu_ctas;
     if (total > 0x7fffffffu) return (int)cudaErrorNotSupported;
-    layer_chain_kernel<<<(unsigned)total, kChainThreads, 0, (cudaStream_t)stream>>>(a);
+    launch_pdl(layer_chain_kernel, dim3((unsigned)total), dim3(kChainThreads), 0, (cudaStream_t)stream, a);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }

@@ -30,6 +30,8 @@ __device__ __forceinline__ vec16 add_vec(const vec16& a, const vec16& b) {
 /* x[i] += y[i] over nvec vectors, then `tail` (< 8) scalar elements. */
 __global__ void __launch_bounds__(kThreads)
 residual_add_vec_kernel(vec16* x, const vec16* y, size_t nvec, __half* tx, const __half* ty, int tail) {
+    pdl_wait();
+    pdl_trigger();
     const size_t base = (size_t)blockIdx.x * (kThreads * kUnroll) + threadIdx.x;
     vec16 xv[kUnroll], yv[kUnroll];
 #pragma unroll
@@ -50,6 +52,8 @@ residual_add_vec_kernel(vec16* x, const vec16* y, size_t nvec, __half* tx, const
 
 __global__ void __launch_bounds__(kThreads)
 residual_add_scalar_kernel(__half* x, const __half* y, size_t n) {
+    pdl_wait();
+    pdl_trigger();
     for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (size_t)gridDim.x * kThreads)
         x[i] = __float2half_rn(__fadd_rn(__half2float(x[i]), __half2float(y[i])));
 }
@@ -58,6 +62,8 @@ residual_add_scalar_kernel(__half* x, const __half* y, size_t n) {
  * bias vectors in registers across the rows it walks. */
 __global__ void __launch_bounds__(kThreads)
 bias_add_vec_kernel(vec16* out, const vec16* bias, int M, int nvec) {
+    pdl_wait();
+    pdl_trigger();
     const int v = blockIdx.x * kThreads + threadIdx.x;
     if (v >= nvec) return;
     const vec16 b = __ldg(bias + v);
@@ -69,6 +75,8 @@ bias_add_vec_kernel(vec16* out, const vec16* bias, int M, int nvec) {
 
 __global__ void __launch_bounds__(kThreads)
 bias_add_scalar_kernel(__half* out, const __half* bias, size_t total, int N) {
+    pdl_wait();
+    pdl_trigger();
     for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (size_t)gridDim.x * kThreads) {
         const int j = (int)(i % (size_t)N);
         out[i] = __float2half_rn(__fadd_rn(__half2float(out[i]), __half2float(bias[j])));
@@ -78,6 +86,8 @@ bias_add_scalar_kernel(__half* out, const __half* bias, size_t total, int N) {
 /* 8 floats (two 16-byte loads) -> one 16-byte store, and back. */
 __global__ void __launch_bounds__(kThreads)
 f32_to_f16_kernel(const float* in, __half* out, size_t n, int vec_ok) {
+    pdl_wait();
+    pdl_trigger();
     const size_t n8 = vec_ok ? n / 8 : 0;
     for (size_t v = (size_t)blockIdx.x * kThreads + threadIdx.x; v < n8; v += (size_t)gridDim.x * kThreads) {
         const float4 a = __ldcs(reinterpret_cast<const float4*>(in) + 2 * v);
@@ -91,6 +101,8 @@ f32_to_f16_kernel(const float* in, __half* out, size_t n, int vec_ok) {
 
 __global__ void __launch_bounds__(kThreads)
 f16_to_f32_kernel(const __half* in, float* out, size_t n, int vec_ok) {
+    pdl_wait();
+    pdl_trigger();
     const size_t n8 = vec_ok ? n / 8 : 0;
     for (size_t v = (size_t)blockIdx.x * kThreads + threadIdx.x; v < n8; v += (size_t)gridDim.x * kThreads) {
         float f[8];
@@ -127,11 +139,9 @@ extern "C" int vvbk_residual_add(void* x, const void* y, size_t n, void* stream)
         size_t blocks = (nvec + per_cta - 1) / per_cta;
         if (blocks == 0) blocks = 1;
         if (blocks > 0x7fffffffu) return (int)cudaErrorInvalidValue;
-        residual_add_vec_kernel<<<(unsigned)blocks, kThreads, 0, s>>>(
-            (vec16*)x, (const vec16*)y, nvec, (__half*)x + nvec * 8, (const __half*)y + nvec * 8, tail);
+        launch_pdl(residual_add_vec_kernel, dim3((unsigned)blocks), dim3(kThreads), 0, s, (vec16*)x, (const vec16*)y, nvec, (__half*)x + nvec * 8, (const __half*)y + nvec * 8, tail);
     } else {
-        residual_add_scalar_kernel<<<capped_blocks(n, kThreads, 148u * 64u), kThreads, 0, s>>>(
-            (__half*)x, (const __half*)y, n);
+        launch_pdl(residual_add_scalar_kernel, dim3(capped_blocks(n, kThreads, 148u * 64u)), dim3(kThreads), 0, s, (__half*)x, (const __half*)y, n);
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
@@ -147,11 +157,10 @@ extern "C" int vvbk_bias_add(void* out, const void* bias, int M, int N, void* st
         const unsigned want = (148u * 16u + bx - 1) / bx;   /* enough CTAs to fill the machine */
         if (by > want) by = want;
         if (by > 65535u) by = 65535u;
-        bias_add_vec_kernel<<<dim3(bx, by), kThreads, 0, s>>>((vec16*)out, (const vec16*)bias, M, nvec);
+        launch_pdl(bias_add_vec_kernel, dim3(bx, by), dim3(kThreads), 0, s, (vec16*)out, (const vec16*)bias, M, nvec);
     } else {
         const size_t total = (size_t)M * (size_t)N;
-        bias_add_scalar_kernel<<<capped_blocks(total, kThreads, 148u * 64u), kThreads, 0, s>>>(
-            (__half*)out, (const __half*)bias, total, N);
+        launch_pdl(bias_add_scalar_kernel, dim3(capped_blocks(total, kThreads, 148u * 64u)), dim3(kThreads), 0, s, (__half*)out, (const __half*)bias, total, N);
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
@@ -161,8 +170,7 @@ extern "C" int vvbk_f32_to_f16(const void* in, void* out, size_t n, void* stream
     cudaStream_t s = (cudaStream_t)stream;
     if (n == 0) return (int)cudaSuccess;
     const int vec_ok = aligned16(in) && aligned16(out);
-    f32_to_f16_kernel<<<capped_blocks(n / 8 + 1, kThreads, 148u * 32u), kThreads, 0, s>>>(
-        (const float*)in, (__half*)out, n, vec_ok);
+    launch_pdl(f32_to_f16_kernel, dim3(capped_blocks(n / 8 + 1, kThreads, 148u * 32u)), dim3(kThreads), 0, s, (const float*)in, (__half*)out, n, vec_ok);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }
@@ -171,8 +179,7 @@ extern "C" int vvbk_f16_to_f32(const void* in, void* out, size_t n, void* stream
     cudaStream_t s = (cudaStream_t)stream;
     if (n == 0) return (int)cudaSuccess;
     const int vec_ok = aligned16(in) && aligned16(out);
-    f16_to_f32_kernel<<<capped_blocks(n / 8 + 1, kThreads, 148u * 32u), kThreads, 0, s>>>(
-        (const __half*)in, (float*)out, n, vec_ok);
+    launch_pdl(f16_to_f32_kernel, dim3(capped_blocks(n / 8 + 1, kThreads, 148u * 32u)), dim3(kThreads), 0, s, (const __half*)in, (float*)out, n, vec_ok);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }

@@ -68,6 +68,8 @@ struct LmHeadArgs {
 template <bool NORM>
 __global__ void __launch_bounds__(kLmThreads, 2)
 lm_head_kernel(const LmHeadArgs a) {
+    pdl_wait();
+    pdl_trigger();
     extern __shared__ __align__(16) float xs[];          /* K floats */
     __shared__ double red[8];
     __shared__ float inv_s;
@@ -164,6 +166,8 @@ lm_head_kernel(const LmHeadArgs a) {
 /* Any K / alignment: one warp per row, scalar halves, x from global memory. */
 __global__ void __launch_bounds__(256)
 lm_head_scalar_kernel(const __half* x, const __half* W, float* logits, int V, int K) {
+    pdl_wait();
+    pdl_trigger();
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= V) return;
     const int lane = threadIdx.x & 31;
@@ -178,6 +182,8 @@ lm_head_scalar_kernel(const __half* x, const __half* W, float* logits, int V, in
 /* Stage 1 of the stand-alone argmax: gridDim.x partials over FP32 logits. */
 __global__ void __launch_bounds__(256)
 argmax_logits_kernel(const float* __restrict__ logits, int V, float* part_v, int* part_i) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ Best wb[8];
     Best best{-FLT_MAX, 0x7fffffff};
     for (int i = blockIdx.x * 256 + threadIdx.x; i < V; i += gridDim.x * 256)
@@ -198,6 +204,8 @@ argmax_logits_kernel(const float* __restrict__ logits, int V, float* part_v, int
  * beat -FLT_MAX) is reported as 0, like the reference's initial value. */
 __global__ void __launch_bounds__(1024)
 argmax_reduce_kernel(const float* part_v, const int* part_i, int n, int* out_token, float* out_value) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ Best wb[32];
     Best best{-FLT_MAX, 0x7fffffff};
     for (int i = threadIdx.x; i < n; i += 1024) best = better(best, Best{part_v[i], part_i[i]});
@@ -248,7 +256,7 @@ extern "C" int vvbk_lm_head(const void* x, const void* norm_w, float eps, const 
                       aligned16(x) && aligned16(W) && aligned16(norm_w);
     if (!fast) {
         if (part_v || norm_w || !logits) return (int)cudaErrorNotSupported;
-        lm_head_scalar_kernel<<<(V + 7) / 8, 256, 0, s>>>((const __half*)x, (const __half*)W, logits, V, K);
+        launch_pdl(lm_head_scalar_kernel, dim3((V + 7) / 8), dim3(256), 0, s, (const __half*)x, (const __half*)W, logits, V, K);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return (int)cudaGetLastError();
     }
@@ -262,21 +270,21 @@ extern "C" int vvbk_lm_head(const void* x, const void* norm_w, float eps, const 
     if (n_partials) *n_partials = grid;      /* entries of part_v / part_i this launch writes */
     LmHeadArgs a{(const vec16*)x, (const vec16*)norm_w, (const vec16*)W, logits, part_v, part_i,
                  V, K, K / 8, rows_per_cta, eps};
-    if (norm_w) lm_head_kernel<true><<<grid, kLmThreads, smem, s>>>(a);
-    else lm_head_kernel<false><<<grid, kLmThreads, smem, s>>>(a);
+    if (norm_w) launch_pdl(lm_head_kernel<true>, dim3(grid), dim3(kLmThreads), smem, s, a);
+    else launch_pdl(lm_head_kernel<false>, dim3(grid), dim3(kLmThreads), smem, s, a);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }
 
 extern "C" int vvbk_argmax_logits(const float* logits, int V, float* part_v, int* part_i, int nparts, void* stream) {
-    argmax_logits_kernel<<<nparts, 256, 0, (cudaStream_t)stream>>>(logits, V, part_v, part_i);
+    launch_pdl(argmax_logits_kernel, dim3(nparts), dim3(256), 0, (cudaStream_t)stream, logits, V, part_v, part_i);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }
 
 extern "C" int vvbk_argmax_reduce(const float* part_v, const int* part_i, int n, int* out_token, float* out_value,
                                   void* stream) {
-    argmax_reduce_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(part_v, part_i, n, out_token, out_value);
+    launch_pdl(argmax_reduce_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, part_v, part_i, n, out_token, out_value);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }

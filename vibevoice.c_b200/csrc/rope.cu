@@ -44,6 +44,8 @@ extern std::atomic<uint64_t> g_launches;
 
 __global__ void __launch_bounds__(kRopeThreads, 4)
 rope_tile_kernel(const __grid_constant__ RopeArgs a) {
+    pdl_wait();
+    pdl_trigger();
     rope_tile_body(a, blockIdx.x, blockIdx.y);
 }
 
@@ -58,6 +60,8 @@ struct RopeScalarArgs {
 
 __global__ void __launch_bounds__(256)
 rope_scalar_kernel(const __grid_constant__ RopeScalarArgs a) {
+    pdl_wait();
+    pdl_trigger();
     const size_t pairs_per_row = (size_t)(a.n_q + a.n_kv) * (size_t)a.half;
     const size_t total = (size_t)a.rows * pairs_per_row;
     const int pos_base = (a.d_position != nullptr ? *a.d_position : a.position_offset);
@@ -103,7 +107,7 @@ extern "C" int vvbk_rope(void* q, void* k, int rows, int n_q_heads, int n_kv_hea
         rope_plan(a, q, k, rows, n_q_heads, n_kv_heads, head_dim, position_offset, d_position, inv_freq,
                   max_passes, &gx, &gy);
         if (gy > 65535u) return (int)cudaErrorInvalidValue;
-        rope_tile_kernel<<<dim3(gx, gy), kRopeThreads, 0, s>>>(a);
+        launch_pdl(rope_tile_kernel, dim3(gx, gy), dim3(kRopeThreads), 0, s, a);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return (int)cudaGetLastError();
     }
@@ -122,7 +126,7 @@ extern "C" int vvbk_rope(void* q, void* k, int rows, int n_q_heads, int n_kv_hea
     const size_t total = (size_t)rows * (size_t)heads * (size_t)half;
     size_t blocks = (total + 255) / 256;
     if (blocks > 148u * 32u) blocks = 148u * 32u;
-    rope_scalar_kernel<<<(unsigned)blocks, 256, 0, s>>>(a);
+    launch_pdl(rope_scalar_kernel, dim3((unsigned)blocks), dim3(256), 0, s, a);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }

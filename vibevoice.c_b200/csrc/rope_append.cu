@@ -59,6 +59,8 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
     __shared__ __align__(16) float sin_s[kRopeTableEntries];
     const RopeArgs& a = A.r;
     const int t = threadIdx.x;
+    pdl_wait();
+    pdl_trigger();
 
     /* The last grid row (blockIdx.y) carries V: no rotation, so no table and
      * no barrier -- a flat copy (+ bias) of kVRowsPerCta rows per CTA into the
@@ -218,7 +220,7 @@ extern "C" int vvbk_rope_append(void* q, void* k, const void* v,
     A.cache_offset = cache_offset;
     A.keep_k = keep_k;
     if (gy > 65535u) return (int)cudaErrorInvalidValue;
-    rope_append_kernel<<<dim3(gx, gy), kRopeThreads, 0, (cudaStream_t)stream>>>(A);
+    launch_pdl(rope_append_kernel, dim3(gx, gy), dim3(kRopeThreads), 0, (cudaStream_t)stream, A);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }

@@ -45,6 +45,8 @@ extern std::atomic<uint64_t> g_launches;
 template <int VPT>
 __global__ void __launch_bounds__(1024)
 row_norm_cta_kernel(const RowNormArgs a) {
+    pdl_wait();
+    pdl_trigger();
     row_norm_body<VPT, 1>(a, blockIdx.x, threadIdx.x, blockDim.x, 0);
 }
 
@@ -62,6 +64,8 @@ struct RowNormGenericArgs {
 
 __global__ void __launch_bounds__(256)
 row_norm_generic_kernel(const RowNormGenericArgs a) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ double red[8];
     __shared__ float inv_s;
     const int t = threadIdx.x;
@@ -115,6 +119,8 @@ row_norm_generic_kernel(const RowNormGenericArgs a) {
 __global__ void __launch_bounds__(256)
 gather_rows_vec_kernel(const vec16* __restrict__ table, const int32_t* __restrict__ ids,
                        vec16* __restrict__ out, int rows, int nvec, int vocab) {
+    pdl_wait();
+    pdl_trigger();
     /* One CTA per row; 4 independent 16-byte loads per thread per trip. */
     const int row = blockIdx.x;
     int id = ids[row];
@@ -153,9 +159,9 @@ static int sm_count() {
 
 static cudaError_t launch_cta(const RowNormArgs& a, int vpt, int threads, cudaStream_t s) {
     switch (vpt) {
-        case 1: row_norm_cta_kernel<1><<<a.rows, threads, 0, s>>>(a); break;
-        case 2: row_norm_cta_kernel<2><<<a.rows, threads, 0, s>>>(a); break;
-        case 4: row_norm_cta_kernel<4><<<a.rows, threads, 0, s>>>(a); break;
+        case 1: launch_pdl(row_norm_cta_kernel<1>, dim3(a.rows), dim3(threads), 0, s, a); break;
+        case 2: launch_pdl(row_norm_cta_kernel<2>, dim3(a.rows), dim3(threads), 0, s, a); break;
+        case 4: launch_pdl(row_norm_cta_kernel<4>, dim3(a.rows), dim3(threads), 0, s, a); break;
         default: return cudaErrorInvalidValue;
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -184,7 +190,7 @@ extern "C" int vvbk_row_norm(const void* src_rows, const void* delta, const int3
         if (ids != nullptr && delta == nullptr && vec_ok) {
             int threads = round_up_warp((nvec + 3) / 4);
             if (threads > 256) threads = 256;
-            gather_rows_vec_kernel<<<rows, threads, 0, s>>>((const vec16*)src_rows, ids, (vec16*)row_out,
+            launch_pdl(gather_rows_vec_kernel, dim3(rows), dim3(threads), 0, s, (const vec16*)src_rows, ids, (vec16*)row_out,
                                                             rows, nvec, vocab);
             g_launches.fetch_add(1, std::memory_order_relaxed);
             return (int)cudaGetLastError();
@@ -192,7 +198,7 @@ extern "C" int vvbk_row_norm(const void* src_rows, const void* delta, const int3
         RowNormGenericArgs g{(const __half*)src_rows, (const __half*)delta, ids, (__half*)row_out,
                              (const __half*)weight, nullptr, rows, hidden, vocab, eps};
         const int resident = sm_count() * 8;
-        row_norm_generic_kernel<<<rows < resident ? rows : resident, 256, 0, s>>>(g);
+        launch_pdl(row_norm_generic_kernel, dim3(rows < resident ? rows : resident), dim3(256), 0, s, g);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return (int)cudaGetLastError();
     }
@@ -221,7 +227,7 @@ extern "C" int vvbk_row_norm(const void* src_rows, const void* delta, const int3
     RowNormGenericArgs g{(const __half*)src_rows, (const __half*)delta, ids, (__half*)row_out,
                          (const __half*)weight, (__half*)normed, rows, hidden, vocab, eps};
     const int resident = sm_count() * 8;
-    row_norm_generic_kernel<<<rows < resident ? rows : resident, 256, 0, s>>>(g);
+    launch_pdl(row_norm_generic_kernel, dim3(rows < resident ? rows : resident), dim3(256), 0, s, g);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }

@@ -47,6 +47,8 @@ __global__ void __launch_bounds__(kSwigluThreads)
 swiglu_vec_kernel(const vec16* gate, const vec16* up, vec16* out,
                   size_t row_vecs, size_t gate_stride, size_t up_stride, size_t out_stride,
                   const __half* tail_gate, const __half* tail_up, __half* tail_out, int tail) {
+    pdl_wait();
+    pdl_trigger();
     const size_t r = blockIdx.y;
     const vec16* g = gate + r * gate_stride;
     const vec16* u = up + r * up_stride;
@@ -65,6 +67,8 @@ swiglu_vec_kernel(const vec16* gate, const vec16* up, vec16* out,
 __global__ void __launch_bounds__(256)
 swiglu_scalar_kernel(const __half* gate, const __half* up, __half* out,
                      size_t row_elems, size_t gate_stride, size_t up_stride, size_t out_stride) {
+    pdl_wait();
+    pdl_trigger();
     const size_t r = blockIdx.y;
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < row_elems; i += (size_t)gridDim.x * 256) {
         const float gf = __half2float(gate[r * gate_stride + i]);
@@ -99,24 +103,24 @@ extern "C" int vvbk_swiglu(const void* gate, const void* up, void* out, size_t n
         const dim3 grid((unsigned)blocks, 1);
 #ifdef VVB_TUNING
         if (unroll == 1)
-            swiglu_vec_kernel<1><<<grid, kSwigluThreads, 0, s>>>(
+            launch_pdl(swiglu_vec_kernel<1>, grid, dim3(kSwigluThreads), 0, s, 
                 (const vec16*)gate, (const vec16*)up, (vec16*)out, nvec, 0, 0, 0, tg, tu, to, tail);
         else if (unroll == 2)
-            swiglu_vec_kernel<2><<<grid, kSwigluThreads, 0, s>>>(
+            launch_pdl(swiglu_vec_kernel<2>, grid, dim3(kSwigluThreads), 0, s, 
                 (const vec16*)gate, (const vec16*)up, (vec16*)out, nvec, 0, 0, 0, tg, tu, to, tail);
         else if (unroll == 8)
-            swiglu_vec_kernel<8><<<grid, kSwigluThreads, 0, s>>>(
+            launch_pdl(swiglu_vec_kernel<8>, grid, dim3(kSwigluThreads), 0, s, 
                 (const vec16*)gate, (const vec16*)up, (vec16*)out, nvec, 0, 0, 0, tg, tu, to, tail);
         else
 #endif
-        swiglu_vec_kernel<kSwigluUnroll><<<grid, kSwigluThreads, 0, s>>>(
-            (const vec16*)gate, (const vec16*)up, (vec16*)out, nvec, 0, 0, 0, tg, tu, to, tail);
+        launch_pdl(swiglu_vec_kernel<kSwigluUnroll>, grid, dim3(kSwigluThreads), 0, s,
+                   (const vec16*)gate, (const vec16*)up, (vec16*)out, nvec, 0, 0, 0, tg, tu, to, tail);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return (int)cudaGetLastError();
     }
     size_t blocks = (n + 255) / 256;
     if (blocks > 148u * 64u) blocks = 148u * 64u;
-    swiglu_scalar_kernel<<<dim3((unsigned)blocks, 1), 256, 0, s>>>(
+    launch_pdl(swiglu_scalar_kernel, dim3((unsigned)blocks, 1), dim3(256), 0, s, 
         (const __half*)gate, (const __half*)up, (__half*)out, n, 0, 0, 0);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
@@ -135,13 +139,13 @@ extern "C" int vvbk_swiglu_fused(const void* gate_up, void* out, int rows, int i
             const size_t row_vecs = (size_t)inter / 8;
             const size_t per_cta = (size_t)kSwigluThreads * kSwigluUnroll;
             const unsigned bx = (unsigned)((row_vecs + per_cta - 1) / per_cta);
-            swiglu_vec_kernel<kSwigluUnroll><<<dim3(bx, (unsigned)nr), kSwigluThreads, 0, s>>>(
+            launch_pdl(swiglu_vec_kernel<kSwigluUnroll>, dim3(bx, (unsigned)nr), dim3(kSwigluThreads), 0, s, 
                 (const vec16*)gu, (const vec16*)(gu + inter), (vec16*)o,
                 row_vecs, 2 * row_vecs, 2 * row_vecs, row_vecs, nullptr, nullptr, nullptr, 0);
         } else {
             unsigned bx = (unsigned)(((size_t)inter + 255) / 256);
             if (bx > 64) bx = 64;
-            swiglu_scalar_kernel<<<dim3(bx, (unsigned)nr), 256, 0, s>>>(
+            launch_pdl(swiglu_scalar_kernel, dim3(bx, (unsigned)nr), dim3(256), 0, s, 
                 gu, gu + inter, o, (size_t)inter, 2 * (size_t)inter, 2 * (size_t)inter, (size_t)inter);
         }
         g_launches.fetch_add(1, std::memory_order_relaxed);

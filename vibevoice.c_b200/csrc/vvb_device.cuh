@@ -83,6 +83,36 @@ __device__ __forceinline__ double warp_sum(double v) {
     return v;
 }
 
+/* Programmatic dependent launch (sm_90+). A kernel launched through
+ * launch_pdl() may be scheduled while the kernel before it on the stream is
+ * still draining; it must call pdl_wait() before its first global-memory
+ * access -- the wait returns when the preceding grid has completed and its
+ * writes are visible, so results are those of an ordinary launch -- and calls
+ * pdl_trigger() to let the kernel after it be scheduled in turn. Both are
+ * no-ops in a kernel launched the ordinary way. What overlaps is the launch
+ * latency and the prologue: for the one-row decode shapes, where a kernel is
+ * a handful of CTAs, that is most of the kernel's cost. */
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#ifdef __CUDACC__
+template <typename... P, typename... A>
+static inline cudaError_t launch_pdl(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                     A&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+#endif
+
 /* 16-byte asynchronous copy global -> shared (LDGSTS), L2-only caching. */
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
     const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
