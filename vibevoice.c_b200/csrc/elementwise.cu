@@ -19,12 +19,7 @@ constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
 
 __device__ __forceinline__ vec16 add_vec(const vec16& a, const vec16& b) {
-    float x[8], y[8];
-    unpack8(a, x);
-    unpack8(b, y);
-#pragma unroll
-    for (int e = 0; e < 8; e++) x[e] = __fadd_rn(x[e], y[e]);
-    return pack8(x);
+    return hadd8(a, b);      /* == widen, add, round to FP16 (vvb_device.cuh) */
 }
 
 /* x[i] += y[i] over nvec vectors, then `tail` (< 8) scalar elements. */

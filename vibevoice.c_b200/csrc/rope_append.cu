@@ -45,12 +45,7 @@ struct RopeAppendArgs {
 };
 
 __device__ __forceinline__ vec16 add_bias_vec(const vec16& x, const vec16& b) {
-    float f[8], g[8];
-    unpack8(x, f);
-    unpack8(b, g);
-#pragma unroll
-    for (int e = 0; e < 8; e++) f[e] = __fadd_rn(f[e], g[e]);
-    return pack8(f);
+    return hadd8(x, b);      /* == widen, add, round to FP16 (vvb_device.cuh) */
 }
 
 __global__ void __launch_bounds__(kRopeThreads, 4)

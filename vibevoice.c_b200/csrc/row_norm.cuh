@@ -90,11 +90,10 @@ __device__ __forceinline__ void row_norm_produce(const RowNormArgs& a, int row, 
         const uint32_t* dw = reinterpret_cast<const uint32_t*>(&dv[j]);
 #pragma unroll
         for (int e = 0; e < 4; e++) {
-            float2 f = unpack2(hw[e]);
-            if (has_delta) {
-                hw[e] = pack2(add2(f, unpack2(dw[e])));   /* round to FP16: this is the new hidden state */
-                f = unpack2(hw[e]);                        /* and the norm sees the rounded values */
-            }
+            /* the new hidden state, rounded to FP16 (== widen, add, narrow: see
+             * hadd2_bits); the norm sees the rounded values */
+            if (has_delta) hw[e] = hadd2_bits(hw[e], dw[e]);
+            const float2 f = unpack2(hw[e]);
             ss = fma((double)f.x, (double)f.x, ss);
             ss = fma((double)f.y, (double)f.y, ss);
         }
