@@ -2,7 +2,7 @@
 seven CUDA files it replaces.
 
 oracle/build_reftests.sh compiles the reference's C sources, its other CUDA
-kernels (GEMMs, attention, KV cache) and four of its tests, unmodified, and
+kernels (GEMMs, attention, KV cache) and five of its tests, unmodified, and
 links them against vibevoice.c_b200/lib/libvvb200.a instead of
 src/cuda/{rmsnorm,rope,swiglu,embedding,conv_vae,act_quant,lm_head}.cu. Each
 program prints its own verdict and exits non-zero on a failed check:
@@ -16,6 +16,8 @@ program prints its own verdict and exits non-zero on a failed check:
                         the GPU (norm, RoPE, SwiGLU, residual adds from
                         src/inference/decoder.c) against its CPU path
   test_skinny           tests/test_skinny.c:179-197: GEMM outputs through vv_bias_add_dev
+  test_w4a16            tests/test_w4a16.c:405-500: INT4 linear layers, bias added by
+                        vv_bias_add_dev (src/cuda/w4a16.cu:930)
 
 Skipped where the programs were not built (the reference is not present on a
 GPU box; the prebuilt programs travel with the tree).
@@ -30,7 +32,7 @@ pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 BIN = os.path.join(ROOT, "oracle", "_ref", "tests")
-PROGRAMS = ["test_int8_linear", "test_decode_position", "test_prefill_append", "test_skinny"]
+PROGRAMS = ["test_int8_linear", "test_decode_position", "test_prefill_append", "test_skinny", "test_w4a16"]
 
 
 @pytest.mark.parametrize("name", PROGRAMS)
