@@ -30,6 +30,7 @@
 #include <atomic>
 #ifdef VVB_TUNING
 #include <cstdlib>
+extern "C" int vvbk_swiglu_bulk(const void* gate, const void* up, void* out, size_t nvec, void* stream, int variant);
 #endif
 
 namespace vvb {
@@ -92,6 +93,9 @@ extern "C" int vvbk_swiglu(const void* gate, const void* up, void* out, size_t n
         int unroll = kSwigluUnroll;
 #ifdef VVB_TUNING
         if (const char* e = getenv("VVB_TUNE_SWIGLU_UNROLL")) unroll = atoi(e);
+        if (const char* e = getenv("VVB_TUNE_SWIGLU_BULK")) {
+            if (atoi(e) != 0 && tail == 0) return vvbk_swiglu_bulk(gate, up, out, nvec, stream, atoi(e));
+        }
 #endif
         const size_t per_cta = (size_t)kSwigluThreads * unroll;
         size_t blocks = (nvec + per_cta - 1) / per_cta;
