@@ -222,10 +222,8 @@ col_absmax_scalar_kernel(const __half* __restrict__ x, int M, int K, float* __re
 
 template <int MODE>
 static cudaError_t launch_q(const ActQuantArgs& a, cudaStream_t s) {
-    int threads = (((a.nvec + 3) / 4) + 31) / 32 * 32;
-    if (threads > 1024) threads = 1024;
-    int vpt = (a.nvec + threads - 1) / threads;
-    if (vpt == 3) vpt = 4;
+    int threads, vpt;
+    row_launch_shape(a.rows, a.nvec, &threads, &vpt);
     switch (vpt) {
         case 1: launch_pdl(act_quant_kernel<1, MODE>, dim3(a.rows), dim3(threads), 0, s, a); break;
         case 2: launch_pdl(act_quant_kernel<2, MODE>, dim3(a.rows), dim3(threads), 0, s, a); break;

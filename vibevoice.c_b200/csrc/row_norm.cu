@@ -207,11 +207,13 @@ extern "C" int vvbk_row_norm(const void* src_rows, const void* delta, const int3
         RowNormArgs a{(const vec16*)src_rows, (const vec16*)delta, ids, (vec16*)row_out,
                       (const vec16*)weight, (vec16*)normed, rows, nvec, hidden, vocab, eps};
         /* A quarter of the row's vectors per thread (128 threads x 4 for a
-         * 3584-wide row): measured fastest from one row to fourteen thousand. */
-        int threads = round_up_warp((nvec + 3) / 4);
-        if (threads > 1024) threads = 1024;
-        int vpt = (nvec + threads - 1) / threads;
-        if (vpt == 3) vpt = 4;
+         * 3584-wide row) is fastest once the grid is several waves deep
+         * (62.2 us against 63.4 and 81.7 for 2 and 1 at 14449 rows). Up to a
+         * few hundred rows the kernel is one wave of latency, and a thread
+         * that owns one vector has a quarter of the serial work: 1.88 against
+         * 2.06 us at one row (the decode shape), 4.27 against 4.55 at 512. */
+        int threads, vpt;
+        row_launch_shape(rows, nvec, &threads, &vpt);
 #ifdef VVB_TUNING
         if (const char* e = getenv("VVB_TUNE_ROWNORM_VPT")) {
             vpt = atoi(e);

@@ -23,6 +23,22 @@ struct RowNormArgs {
     float eps;
 };
 
+/* Launch shape of the one-CTA-per-row kernels (row norm, int8 quantizers):
+ * threads per row and 16-byte vectors per thread (1, 2 or 4). Deep grids take
+ * four vectors per thread; grids of at most kLatencyRows rows (about one wave
+ * on a 148-SM part) are bound by one row's latency and take one vector per
+ * thread when the row fits a CTA that way. */
+constexpr int kLatencyRows = 592;
+static inline void row_launch_shape(int rows, int nvec, int* threads, int* vpt) {
+    const int per_thread = (rows <= kLatencyRows && nvec <= 1024) ? 1 : 4;
+    int t = (((nvec + per_thread - 1) / per_thread) + 31) / 32 * 32;
+    if (t > 1024) t = 1024;
+    int v = (nvec + t - 1) / t;
+    if (v == 3) v = 4;
+    *threads = t;
+    *vpt = v;
+}
+
 __device__ __forceinline__ float inv_rms(double ss, int hidden, float eps) {
     const float mean = (float)(ss / (double)hidden);
     return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
