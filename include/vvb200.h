@@ -7,8 +7,9 @@
  * The first group of functions has exactly the names, argument lists and
  * argument meaning of the reference's accelerator op set for this path, so a
  * build of the reference that leaves out its own rmsnorm.cu / rope.cu /
- * swiglu.cu / embedding.cu / conv_vae.cu and links this library resolves the
- * same symbols (the reference picks its backend at link time:
+ * swiglu.cu / embedding.cu / conv_vae.cu / act_quant.cu / lm_head.cu and
+ * links this library resolves the same symbols (the reference picks its
+ * backend at link time:
  * include/vibevoice/device.h:11-14). The second group (vvb_*) is additive:
  * fused forms that save HBM passes, a host-buffer pipeline, and the row
  * partition used to shard tokens over the GPUs of one box.
@@ -20,6 +21,12 @@
  *   - `void* stream` is a cudaStream_t; NULL is the legacy default stream;
  *   - work is enqueued and the call returns; nothing synchronises, allocates,
  *     frees or keeps a pointer, so every *_dev call may be stream-captured;
+ *   - kernels are launched with the programmatic stream serialization
+ *     attribute and wait for the preceding grid at their first instruction:
+ *     ordering on the stream is that of an ordinary launch (also against
+ *     kernels that are not this library's), only launch latency overlaps;
+ *     captured, a kernel-to-kernel dependency becomes a programmatic graph
+ *     edge (CUDA 12.3 or later);
  *   - calls are re-entrant: no file-scope mutable state;
  *   - the return value is a vv_status_t code; nothing throws, aborts or logs;
  *   - rows == 0 / n == 0 is VV_OK and launches nothing;
