@@ -225,6 +225,32 @@ vv_status_t vvb_rope_qk_append_dev(void* q, void* k, const void* v,
                                    int position_offset, int cache_offset, const int* d_position,
                                    float theta, int keep_k, void* stream);
 
+/** kv_format values of vvb_rope_qk_append_fp8_dev: numerically the reference's
+ *  vv_kv_format_t (include/vibevoice/kv_quant.h:34-36). */
+#define VVB_KV_FP8_E4M3 1
+#define VVB_KV_FP8_E5M2 2
+
+/** vvb_rope_qk_append_dev for the FP8 KV cache: the same single launch, but the
+ *  cache rows receive the reference's software FP8 byte of every value (one
+ *  byte per element, [max_len, n_kv_heads * head_dim] uint8 per layer -- the
+ *  layout vv_kv_quant_store_dev writes with no page table,
+ *  src/cuda/kv_quant.cu:60-83; encodings src/cuda/kv_codec.cuh:68-120: mantissa
+ *  rounded to nearest even, saturating at +-448 / +-57344, subnormals rounded
+ *  half up, NaN stored as zero). Equivalent, byte for byte, to vv_bias_add_dev
+ *  x3, vv_rope_dev x2 and vv_kv_quant_store_dev on the FP16 results: K is
+ *  rounded to FP16 after the rotation, then k_ref (FP16 [n_kv_heads *
+ *  head_dim], the layer's reference key, NULL when the cache keeps none) is
+ *  subtracted in float and the difference encoded; V is encoded as it is.
+ *  Building the reference key (the mean over the first chunk) stays a call of
+ *  its own. kv_format is VVB_KV_FP8_E4M3 or VVB_KV_FP8_E5M2 (anything else:
+ *  VV_ERR_UNSUPPORTED). Other arguments as vvb_rope_qk_append_dev. */
+vv_status_t vvb_rope_qk_append_fp8_dev(void* q, void* k, const void* v,
+                                       const void* q_bias, const void* k_bias, const void* v_bias,
+                                       void* k_store, void* v_store, const void* k_ref,
+                                       int rows, int n_q_heads, int n_kv_heads, int head_dim,
+                                       int position_offset, int cache_offset, const int* d_position,
+                                       float theta, int kv_format, int keep_k, void* stream);
+
 /** Final RMSNorm + LM head + greedy argmax in two launches (the reference
  *  issues four: vv_rmsnorm_dev, vv_lm_head_gemv_dev and vv_argmax_dev's two,
  *  src/inference/pipeline.c:1962-1978). x[K] is the last hidden row when

@@ -133,6 +133,36 @@ class _Restated:
         assert st == 0, st
         return logits, int(tok.value), float(val.value)
 
+    def fp8_encode(self, x_f32, fmt):
+        """The reference's software FP8 byte of each float (fmt 1 = E4M3, 2 = E5M2)."""
+        L = self.lib
+        L.orc_fp8_encode.restype = C.c_uint8
+        L.orc_fp8_encode.argtypes = [C.c_float, C.c_int]
+        flat = np.ascontiguousarray(x_f32, dtype=np.float32).reshape(-1)
+        return np.array([L.orc_fp8_encode(float(v), int(fmt)) for v in flat], np.uint8).reshape(np.shape(x_f32))
+
+    def fp8_decode(self, codes, fmt):
+        L = self.lib
+        L.orc_fp8_decode.restype = C.c_float
+        L.orc_fp8_decode.argtypes = [C.c_uint8, C.c_int]
+        flat = np.ascontiguousarray(codes, dtype=np.uint8).reshape(-1)
+        return np.array([L.orc_fp8_decode(int(v), int(fmt)) for v in flat], np.float32).reshape(np.shape(codes))
+
+    def kv_store_fp8(self, x_f16, ref_f16, fmt, first_row=0, out=None):
+        """FP16 [n_pos, width] (minus ref [width], in float) -> FP8 bytes written to rows
+        first_row.. of `out` (uint8 [max_len, width]; allocated [first_row + n_pos, width] if None)."""
+        L = self.lib
+        L.orc_kv_store_fp8.argtypes = [_u16p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        x = _as_u16(x_f16)
+        n_pos, width = x.shape[0], int(np.prod(x.shape[1:]))
+        if out is None:
+            out = np.zeros((first_row + n_pos, width), np.uint8)
+        r = _as_u16(ref_f16) if ref_f16 is not None else None
+        st = L.orc_kv_store_fp8(_ptr(x, _u16p), r.ctypes.data if r is not None else None, n_pos, width,
+                                int(first_row), int(fmt), out.ctypes.data)
+        assert st == 0, st
+        return out
+
     def quant_act_q8(self, x_f32, layout, want_xsum=True):
         """Per-token int8 quantizer on FP32 rows [M, K]: (xq int8 [M,K],
         sx float32 [M], xsum int32 [M, K/32] or None)."""

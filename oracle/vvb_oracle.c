@@ -352,3 +352,78 @@ int orc_quant_act_q8(const float* x, int M, int K, int layout,
     }
     return ORC_OK;
 }
+
+/* ---- software FP8 of the KV cache (src/cuda/kv_codec.cuh:68-120) ----------
+ * The reference stores a float as one byte: sign, E exponent bits (bias B),
+ * M mantissa bits; E4M3 has B = 7 and tops out at 448 (0x7E), E5M2 has B = 15
+ * and tops out at 57344 (0x7B). Step by step, as kv_codec.cuh does it:
+ *   zero or NaN -> the sign bit alone;
+ *   a >= 464 (E4M3) / 61440 (E5M2) -> the largest finite code;
+ *   exponent below the normal range -> q = (int)(a * 2^(M+B-1) + 0.5f) in float
+ *     arithmetic, capped at 2^M (which is the smallest normal's code);
+ *   else take the top M mantissa bits, round on the remainder to nearest, ties
+ *     to even, carry into the exponent, and saturate if the exponent left the
+ *     range.
+ * fmt: 1 = E4M3, 2 = E5M2 (include/vibevoice/kv_quant.h:34-36). */
+uint8_t orc_fp8_encode(float f, int fmt) {
+    const int M = (fmt == 1) ? 3 : 2;
+    const int bias = (fmt == 1) ? 7 : 15;
+    const int emax = (fmt == 1) ? 8 : 15;
+    const uint8_t top = (fmt == 1) ? 0x7E : 0x7B;
+    const float sat = (fmt == 1) ? 464.0f : 61440.0f;
+    uint32_t b;
+    memcpy(&b, &f, 4);
+    const uint8_t s = (uint8_t)((b >> 24) & 0x80u);
+    const float a = fabsf(f);
+    if (!(a > 0.0f)) return s;
+    if (a >= sat) return (uint8_t)(s | top);
+    int e = (int)((b >> 23) & 0xFFu) - 127;
+    if (e < 1 - bias) {
+        const float scaled = a * ldexpf(1.0f, M + bias - 1);   /* exact: a power of two */
+        int q = (int)(scaled + 0.5f);
+        if (q > (1 << M)) q = 1 << M;
+        return (uint8_t)(s | q);
+    }
+    const uint32_t frac = b & 0x7FFFFFu;
+    const int drop = 23 - M;
+    uint32_t keep = frac >> drop;
+    const uint32_t rem = frac & ((1u << drop) - 1u);
+    const uint32_t half = 1u << (drop - 1);
+    if (rem > half || (rem == half && (keep & 1u))) {
+        keep++;
+        if (keep == (1u << M)) { keep = 0; e++; }
+    }
+    if (e > emax) return (uint8_t)(s | top);
+    return (uint8_t)(s | ((uint32_t)(e + bias) << M) | keep);
+}
+
+/* The store of src/cuda/kv_quant.cu:60-83 with no page table: x is FP16
+ * [n_pos, n_kv_heads * head_dim]; ref (may be null) FP16 [n_kv_heads * head_dim]
+ * is subtracted in float before encoding; out[(first_row + p) * width + j]. */
+int orc_kv_store_fp8(const uint16_t* x_f16, const uint16_t* ref_f16, int n_pos, int width,
+                     int first_row, int fmt, uint8_t* out) {
+    if (!x_f16 || !out) return ORC_ERR_NULL_PTR;
+    if (n_pos < 0 || width <= 0 || first_row < 0 || (fmt != 1 && fmt != 2)) return ORC_ERR_INVALID_ARG;
+    for (int p = 0; p < n_pos; p++) {
+        for (int j = 0; j < width; j++) {
+            float v = orc_half_to_float(x_f16[(size_t)p * width + j]);
+            if (ref_f16) v -= orc_half_to_float(ref_f16[j]);
+            /* On the device every NaN that reaches the encoder is the canonical
+             * one, whose sign bit is clear (the FP16 -> float conversion and the
+             * float subtraction both produce it), so a NaN of either sign is
+             * stored as 0x00: the golden bytes of the reference kernel show it. */
+            out[(size_t)(first_row + p) * width + j] = (v != v) ? (uint8_t)0 : orc_fp8_encode(v, fmt);
+        }
+    }
+    return ORC_OK;
+}
+
+/* Decoding (src/cuda/kv_codec.cuh:91-97,122-128), for round-trip checks. */
+float orc_fp8_decode(uint8_t v, int fmt) {
+    const int M = (fmt == 1) ? 3 : 2;
+    const int bias = (fmt == 1) ? 7 : 15;
+    const int e = (v >> M) & ((fmt == 1) ? 0xF : 0x1F);
+    const int m = v & ((1 << M) - 1);
+    const float r = (e == 0) ? ldexpf((float)m, 1 - bias - M) : ldexpf(1.0f + (float)m / (float)(1 << M), e - bias);
+    return (v & 0x80) ? -r : r;
+}

@@ -1,0 +1,78 @@
+/*
+ * fp8_kv.cuh -- the reference's software FP8 encodings of the KV cache
+ * (include/vibevoice/kv_quant.h:34-36: VV_KV_FP8_E4M3 = 1, VV_KV_FP8_E5M2 = 2;
+ * the byte each float maps to is defined by src/cuda/kv_codec.cuh:68-120).
+ *
+ * The mapping, for sign s, magnitude a = |f| (M mantissa bits, exponent bias
+ * B, smallest normal 2^(1-B)):
+ *   a == 0 or NaN          -> s                      (NaN is stored as zero)
+ *   a <  2^(1-B)           -> s | min(int(a * 2^(M+B-1) + 0.5), 2^M)
+ *                             fixed point, round half UP, in float arithmetic
+ *   otherwise              -> mantissa rounded to M bits, nearest even, carry
+ *                             into the exponent, then clamped to the largest
+ *                             finite code (E4M3: 0x7E = 448, E5M2: 0x7B = 57344)
+ * The clamp also covers the reference's early saturation tests (a >= 464,
+ * a >= 61440): those are exactly the magnitudes whose rounded code would
+ * exceed the largest finite one.
+ *
+ * Here the normal range is one integer add on the bit pattern (the rounding
+ * increment 2^(22-M) - 1 + the kept LSB, so the carry runs into the exponent
+ * field by itself), a shift, a re-bias and a min; no hardware FP8 conversion
+ * is used because cvt.e4m3x2 rounds the subnormal range to even and stores a
+ * NaN as NaN, which would differ from the reference's bytes.
+ */
+#pragma once
+#include "vvb_device.cuh"
+
+namespace vvb {
+
+enum { KV_RAW = 0, KV_E4M3 = 1, KV_E5M2 = 2 };
+
+template <int FMT>
+__device__ __forceinline__ uint32_t fp8_encode(float f) {
+    constexpr int M = (FMT == KV_E4M3) ? 3 : 2;
+    constexpr int BIAS = (FMT == KV_E4M3) ? 7 : 15;
+    constexpr uint32_t MAX_CODE = (FMT == KV_E4M3) ? 0x7Eu : 0x7Bu;
+    constexpr uint32_t MIN_NORMAL = (uint32_t)(127 + 1 - BIAS) << 23;      /* bits of 2^(1-BIAS) */
+    const float sub_scale = (FMT == KV_E4M3) ? 512.0f : 65536.0f;          /* 2^(M+BIAS-1) */
+
+    const uint32_t b = __float_as_uint(f);
+    const uint32_t s = (b >> 24) & 0x80u;
+    const uint32_t ab = b & 0x7fffffffu;
+    const float a = __uint_as_float(ab);
+    if (!(a > 0.0f)) return s;
+    uint32_t code;
+    if (ab < MIN_NORMAL) {
+        code = (uint32_t)__float2int_rz(__fmaf_rn(a, sub_scale, 0.5f));
+        code = min(code, 1u << M);
+    } else {
+        const uint32_t r = ab + ((1u << (22 - M)) - 1u) + ((ab >> (23 - M)) & 1u);
+        code = (r >> (23 - M)) - ((uint32_t)(127 - BIAS) << M);
+        code = min(code, MAX_CODE);
+    }
+    return s | code;
+}
+
+/* Eight FP16 values (optionally minus eight FP16 reference values, the
+ * subtraction in float as src/cuda/kv_quant.cu:66-73 does it) -> eight bytes,
+ * element e in byte e. */
+template <int FMT>
+__device__ __forceinline__ uint2 fp8_encode8(const vec16& x, const vec16* ref) {
+    float f[8];
+    unpack8(x, f);
+    if (ref != nullptr) {
+        float r[8];
+        unpack8(*ref, r);
+#pragma unroll
+        for (int e = 0; e < 8; e++) f[e] = __fsub_rn(f[e], r[e]);
+    }
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        lo |= fp8_encode<FMT>(f[e]) << (8 * e);
+        hi |= fp8_encode<FMT>(f[e + 4]) << (8 * e);
+    }
+    return make_uint2(lo, hi);
+}
+
+}  // namespace vvb

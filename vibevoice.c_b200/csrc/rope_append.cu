@@ -21,7 +21,17 @@
  * the rotation is rope.cuh's, the append is a bit copy. The cache is the
  * reference's raw FP16 layout: one [max_len, n_kv_heads * head_dim] array per
  * layer for K and one for V (src/inference/kv_cache.c:229-232).
+ *
+ * FP8 caches (template FMT = KV_E4M3 / KV_E5M2): the same launch, but what is
+ * stored is the reference's software FP8 byte of each value (fp8_kv.cuh), one
+ * byte per element in the same [max_len, n_kv_heads * head_dim] order
+ * (src/cuda/kv_quant.cu:60-83 with a null page table). K is rounded to FP16
+ * after the rotation, as the separate vv_rope_dev would have stored it, has
+ * the layer's reference key subtracted in float when the cache keeps one
+ * (kv_quant.cu:68-73), and is encoded; V is encoded as it is. The cache write
+ * shrinks from 4096 to 2048 bytes per 7B token.
  */
+#include "fp8_kv.cuh"
 #include "rope.cuh"
 
 #include <atomic>
@@ -40,6 +50,7 @@ struct RopeAppendArgs {
     const vec16* q_bias;      /* each may be null */
     const vec16* k_bias;
     const vec16* v_bias;
+    const vec16* k_ref;       /* FP8 only: [n_kv_heads * head_dim] FP16 subtracted from K; may be null */
     int cache_offset;         /* cache row of row 0 (when r.d_position is null) */
     int keep_k;               /* also write the rotated K back in place */
 };
@@ -48,6 +59,7 @@ __device__ __forceinline__ vec16 add_bias_vec(const vec16& x, const vec16& b) {
     return hadd8(x, b);      /* == widen, add, round to FP16 (vvb_device.cuh) */
 }
 
+template <int FMT>
 __global__ void __launch_bounds__(kRopeThreads, 4)
 rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
     __shared__ __align__(16) float cos_s[kRopeTableEntries];
@@ -71,7 +83,9 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
             const int cv = it - rl * cols_v;
             vec16 x = ld_stream(A.v + (size_t)(row0v + rl) * cols_v + cv);
             if (A.v_bias) x = add_bias_vec(x, __ldg(A.v_bias + cv));
-            st_stream(A.v_cache + (size_t)(cache_first_v + row0v + rl) * cols_v + cv, x);
+            const size_t at = (size_t)(cache_first_v + row0v + rl) * cols_v + cv;
+            if (FMT == KV_RAW) st_stream(A.v_cache + at, x);
+            else __stcs(reinterpret_cast<uint2*>(A.v_cache) + at, fp8_encode8<FMT>(x, nullptr));
         }
         return;
     }
@@ -98,6 +112,8 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
     const vec16* bias = nullptr;
     size_t stride;
     int dst_row_first = 0;
+    bool to_cache = false;
+    vec16 rlo = make_uint4(0, 0, 0, 0), rhi = make_uint4(0, 0, 0, 0);     /* reference key (FP8) */
     if (head < a.n_q) {
         const size_t off = (size_t)head * vph + vec;
         stride = (size_t)a.n_q * vph;
@@ -110,6 +126,11 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
         src = a.k + off;
         dst = A.k_cache + off;
         dst_row_first = cache_first;
+        to_cache = true;
+        if (FMT != KV_RAW && A.k_ref != nullptr && col_ok) {
+            rlo = __ldg(A.k_ref + off);
+            rhi = __ldg(A.k_ref + off + a.hvn);
+        }
         if (A.keep_k) dst_keep = a.k + off;
         if (A.k_bias) bias = A.k_bias + off;
     }
@@ -170,9 +191,18 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
             xlo = pack8(y0);
             xhi = pack8(y1);
         }
-        vec16* d = dst + (size_t)(dst_row_first + row0 + rl) * stride;
-        st_stream(d, xlo);
-        st_stream(d + a.hvn, xhi);
+        if (FMT != KV_RAW && to_cache) {
+            /* one byte per element: vector i of the row is 8 bytes at uint2 index i */
+            uint2* d8 = reinterpret_cast<uint2*>(A.k_cache) +
+                        ((size_t)(dst_row_first + row0 + rl) * stride + (size_t)(dst - A.k_cache));
+            const bool sub = A.k_ref != nullptr;
+            __stcs(d8, fp8_encode8<FMT>(xlo, sub ? &rlo : nullptr));
+            __stcs(d8 + a.hvn, fp8_encode8<FMT>(xhi, sub ? &rhi : nullptr));
+        } else {
+            vec16* d = dst + (size_t)(dst_row_first + row0 + rl) * stride;
+            st_stream(d, xlo);
+            st_stream(d + a.hvn, xhi);
+        }
         if (dst_keep != nullptr) {
             vec16* d2 = dst_keep + (size_t)(row0 + rl) * stride;
             st_stream(d2, xlo);
@@ -194,7 +224,9 @@ extern "C" int vvbk_rope_append(void* q, void* k, const void* v,
                                 void* k_cache, void* v_cache,
                                 int rows, int n_q_heads, int n_kv_heads, int head_dim,
                                 int position_offset, int cache_offset, const int* d_position,
-                                const float* inv_freq, int keep_k, void* stream) {
+                                const float* inv_freq, int keep_k, int kv_format, const void* k_ref,
+                                void* stream) {
+    if (kv_format < KV_RAW || kv_format > KV_E5M2 || !aligned16(k_ref)) return (int)cudaErrorNotSupported;
     if (head_dim % 16 != 0 || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(q_bias) ||
         !aligned16(k_bias) || !aligned16(v_bias) || !aligned16(k_cache) || !aligned16(v_cache))
         return (int)cudaErrorNotSupported;
@@ -212,10 +244,15 @@ extern "C" int vvbk_rope_append(void* q, void* k, const void* v,
     A.q_bias = (const vec16*)q_bias;
     A.k_bias = (const vec16*)k_bias;
     A.v_bias = (const vec16*)v_bias;
+    A.k_ref = (kv_format == KV_RAW) ? nullptr : (const vec16*)k_ref;
     A.cache_offset = cache_offset;
     A.keep_k = keep_k;
     if (gy > 65535u) return (int)cudaErrorInvalidValue;
-    launch_pdl(rope_append_kernel, dim3(gx, gy), dim3(kRopeThreads), 0, (cudaStream_t)stream, A);
+    const dim3 grid(gx, gy), block(kRopeThreads);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (kv_format == KV_E4M3) launch_pdl(rope_append_kernel<KV_E4M3>, grid, block, 0, s, A);
+    else if (kv_format == KV_E5M2) launch_pdl(rope_append_kernel<KV_E5M2>, grid, block, 0, s, A);
+    else launch_pdl(rope_append_kernel<KV_RAW>, grid, block, 0, s, A);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }

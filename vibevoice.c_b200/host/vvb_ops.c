@@ -63,12 +63,12 @@ vv_status_t vvb_rope_qk_dev(void* q, void* k, int rows, int n_q_heads, int n_kv_
                                position_offset, d_position, inv_freq, stream));
 }
 
-vv_status_t vvb_rope_qk_append_dev(void* q, void* k, const void* v,
-                                   const void* q_bias, const void* k_bias, const void* v_bias,
-                                   void* k_cache, void* v_cache,
-                                   int rows, int n_q_heads, int n_kv_heads, int head_dim,
-                                   int position_offset, int cache_offset, const int* d_position,
-                                   float theta, int keep_k, void* stream) {
+static vv_status_t rope_qk_append(void* q, void* k, const void* v,
+                                  const void* q_bias, const void* k_bias, const void* v_bias,
+                                  void* k_cache, void* v_cache, const void* k_ref,
+                                  int rows, int n_q_heads, int n_kv_heads, int head_dim,
+                                  int position_offset, int cache_offset, const int* d_position,
+                                  float theta, int kv_format, int keep_k, void* stream) {
     if (!q || !k || !v || !k_cache || !v_cache) return VV_ERR_NULL_PTR;
     if (rows < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || cache_offset < 0)
         return VV_ERR_INVALID_ARG;
@@ -78,9 +78,35 @@ vv_status_t vvb_rope_qk_append_dev(void* q, void* k, const void* v,
     fill_inv_freq(inv_freq, head_dim, theta);
     const int err = vvbk_rope_append(q, k, v, q_bias, k_bias, v_bias, k_cache, v_cache, rows,
                                      n_q_heads, n_kv_heads, head_dim, position_offset, cache_offset,
-                                     d_position, inv_freq, keep_k, stream);
+                                     d_position, inv_freq, keep_k, kv_format, k_ref, stream);
     if (err == 801) return VV_ERR_UNSUPPORTED;   /* cudaErrorNotSupported: not vectorisable */
     return from_cuda(err);
+}
+
+vv_status_t vvb_rope_qk_append_dev(void* q, void* k, const void* v,
+                                   const void* q_bias, const void* k_bias, const void* v_bias,
+                                   void* k_cache, void* v_cache,
+                                   int rows, int n_q_heads, int n_kv_heads, int head_dim,
+                                   int position_offset, int cache_offset, const int* d_position,
+                                   float theta, int keep_k, void* stream) {
+    return rope_qk_append(q, k, v, q_bias, k_bias, v_bias, k_cache, v_cache, NULL, rows, n_q_heads,
+                          n_kv_heads, head_dim, position_offset, cache_offset, d_position, theta,
+                          0, keep_k, stream);
+}
+
+vv_status_t vvb_rope_qk_append_fp8_dev(void* q, void* k, const void* v,
+                                       const void* q_bias, const void* k_bias, const void* v_bias,
+                                       void* k_store, void* v_store, const void* k_ref,
+                                       int rows, int n_q_heads, int n_kv_heads, int head_dim,
+                                       int position_offset, int cache_offset, const int* d_position,
+                                       float theta, int kv_format, int keep_k, void* stream) {
+    /* the reference's vv_kv_format_t: 1 = FP8 E4M3, 2 = FP8 E5M2 (its own FP8
+     * store takes head_dim 128 only, src/cuda/kv_quant.cu:527; the byte layout
+     * is defined for any head_dim and this kernel takes multiples of 16) */
+    if (kv_format != VVB_KV_FP8_E4M3 && kv_format != VVB_KV_FP8_E5M2) return VV_ERR_UNSUPPORTED;
+    return rope_qk_append(q, k, v, q_bias, k_bias, v_bias, k_store, v_store, k_ref, rows, n_q_heads,
+                          n_kv_heads, head_dim, position_offset, cache_offset, d_position, theta,
+                          kv_format, keep_k, stream);
 }
 
 vv_status_t vv_rope_dev(void* x, int seq_len, int n_heads, int head_dim,

@@ -84,6 +84,8 @@ SIGNATURES = {
     "vvb_rope_qk_dev": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp]),
     "vvb_embedding_rmsnorm_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
     "vvb_rope_qk_append_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _f, _i, _vp]),
+    "vvb_rope_qk_append_fp8_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _f,
+                                        _i, _i, _vp]),
     "vvb_swiglu_dev": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "vvb_residual_add_dev": (_i, [_vp, _vp, _sz, _vp]),
     "vvb_layer_chain_dev": (_i, [C.POINTER(LayerChain), _vp]),
@@ -253,6 +255,18 @@ def vvb_rope_qk_append_dev(q, k, v, q_bias, k_bias, v_bias, k_cache, v_cache, ro
                                        _ptr(k_cache), _ptr(v_cache), rows, n_q_heads, n_kv_heads, head_dim,
                                        position_offset, cache_offset, _ptr(d_position), theta, keep_k,
                                        _stream(stream))
+
+
+VVB_KV_FP8_E4M3, VVB_KV_FP8_E5M2 = 1, 2
+
+
+def vvb_rope_qk_append_fp8_dev(q, k, v, q_bias, k_bias, v_bias, k_store, v_store, k_ref, rows, n_q_heads,
+                               n_kv_heads, head_dim, position_offset, cache_offset, d_position, theta, kv_format,
+                               keep_k=0, stream=None) -> int:
+    return _lib.vvb_rope_qk_append_fp8_dev(_ptr(q), _ptr(k), _ptr(v), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
+                                           _ptr(k_store), _ptr(v_store), _ptr(k_ref), rows, n_q_heads,
+                                           n_kv_heads, head_dim, position_offset, cache_offset,
+                                           _ptr(d_position), theta, kv_format, keep_k, _stream(stream))
 
 
 def vvb_embedding_rmsnorm_dev(table, ids, hidden_out, weight, normed_out, rows, hidden_size, vocab, eps,
