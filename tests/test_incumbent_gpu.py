@@ -44,6 +44,9 @@ def libs():
     ref.vv_swiglu_q8_dev.argtypes = [vp, vp, i, i, i, vp, vp, vp, vp]
     ref.vv_lm_head_gemv_dev.argtypes = [vp, vp, vp, i, i, vp]
     ref.vv_argmax_dev.argtypes = [vp, i, vp, vp, vp, vp, vp]
+    ref.vv_bias_add_dev.argtypes = [vp, vp, i, i, vp]
+    if hasattr(ref, "vv_kv_quant_store_dev"):
+        ref.vv_kv_quant_store_dev.argtypes = [vp, vp, vp, vp, vp, vp, vp, C.c_bool, i, i, i, vp, i, i, vp]
     return vvb200, ref
 
 
@@ -184,6 +187,35 @@ def test_q8_vs_incumbent(libs):
             theirs = time_graph(lambda k, s: ref.vv_swiglu_q8_dev(p(xs[k]), p(us[k]), rows, K, 0, p(q[k]), p(sx), p(xsum), s), n)
         record(f"{kind} [{rows},{K}]", ours, theirs)
         assert ours < theirs
+
+
+def test_fp8_kv_append_vs_incumbent(libs):
+    """Bias adds + RoPE + FP8 (E4M3) cache store: one launch here, seven in the
+    reference (vv_bias_add_dev x3, vv_rope_dev x2, vv_kv_quant_store_dev's two kernels)."""
+    vv, ref = libs
+    if not hasattr(ref, "vv_kv_quant_store_dev"):
+        pytest.skip("the reference's kv_quant.cu is not in the compiled library")
+    rows = 14449
+    n = nsets(rows * (2 * NQ + 2 * NKV) * HD * 2)
+    qs, ks, vs = ([rn(rows, h, HD) for _ in range(n)] for h in (NQ, NKV, NKV))
+    kst = [torch.empty(rows, NKV * HD, device="cuda", dtype=torch.uint8) for _ in range(n)]
+    vst = [torch.empty(rows, NKV * HD, device="cuda", dtype=torch.uint8) for _ in range(n)]
+    bq, bk, bv, kref = rn(NQ * HD), rn(NKV * HD), rn(NKV * HD), rn(NKV * HD)
+    ours = time_graph(lambda k, s: vv.vvb_rope_qk_append_fp8_dev(p(qs[k]), p(ks[k]), p(vs[k]), p(bq), p(bk), p(bv),
+                                                                 p(kst[k]), p(vst[k]), p(kref), rows, NQ, NKV, HD, 0, 0,
+                                                                 None, 1e6, 1, 0, s), n)
+
+    def ref_seq(k, s):
+        assert ref.vv_bias_add_dev(p(qs[k]), p(bq), rows, NQ * HD, s) == 0
+        assert ref.vv_bias_add_dev(p(ks[k]), p(bk), rows, NKV * HD, s) == 0
+        assert ref.vv_bias_add_dev(p(vs[k]), p(bv), rows, NKV * HD, s) == 0
+        assert ref.vv_rope_dev(p(qs[k]), rows, NQ, HD, 0, None, 1e6, s) == 0
+        assert ref.vv_rope_dev(p(ks[k]), rows, NKV, HD, 0, None, 1e6, s) == 0
+        assert ref.vv_kv_quant_store_dev(p(ks[k]), p(vs[k]), p(kst[k]), p(vst[k]), None, None, p(kref), False,
+                                         NKV, HD, 0, None, rows, 1, s) == 0
+    theirs = time_graph(ref_seq, n)
+    record(f"bias + rope + fp8 e4m3 kv store [{rows},28+4+4,128]", ours, theirs)
+    assert ours < theirs
 
 
 def test_lm_head_vs_incumbent(libs):

@@ -36,21 +36,24 @@ __device__ __forceinline__ uint32_t fp8_encode(float f) {
     constexpr uint32_t MIN_NORMAL = (uint32_t)(127 + 1 - BIAS) << 23;      /* bits of 2^(1-BIAS) */
     const float sub_scale = (FMT == KV_E4M3) ? 512.0f : 65536.0f;          /* 2^(M+BIAS-1) */
 
+    /* Branch-free: both ranges are evaluated and one is selected (lanes of a
+     * warp hold values of both ranges nearly always, so a branch would run
+     * both sides anyway, plus the divergence). */
     const uint32_t b = __float_as_uint(f);
-    const uint32_t s = (b >> 24) & 0x80u;
     const uint32_t ab = b & 0x7fffffffu;
     const float a = __uint_as_float(ab);
-    if (!(a > 0.0f)) return s;
-    uint32_t code;
-    if (ab < MIN_NORMAL) {
-        code = (uint32_t)__float2int_rz(__fmaf_rn(a, sub_scale, 0.5f));
-        code = min(code, 1u << M);
-    } else {
-        const uint32_t r = ab + ((1u << (22 - M)) - 1u) + ((ab >> (23 - M)) & 1u);
-        code = (r >> (23 - M)) - ((uint32_t)(127 - BIAS) << M);
-        code = min(code, MAX_CODE);
-    }
-    return s | code;
+    /* below the smallest normal (zero included): int(a * scale + 0.5), truncated.
+     * Adding 2^23 toward zero leaves that integer in the low mantissa bits. */
+    const float t = __fmaf_rn(a, sub_scale, 0.5f);
+    uint32_t sub = __float_as_uint(__fadd_rz(t, 8388608.0f)) & 0xFu;
+    sub = min(sub, 1u << M);
+    /* normal range */
+    const uint32_t r = ab + ((1u << (22 - M)) - 1u) + ((ab >> (23 - M)) & 1u);
+    uint32_t nor = (r >> (23 - M)) - ((uint32_t)(127 - BIAS) << M);
+    nor = min(nor, MAX_CODE);
+    uint32_t code = (ab < MIN_NORMAL) ? sub : nor;
+    code = (ab > 0x7f800000u) ? 0u : code;                       /* NaN */
+    return ((b >> 24) & 0x80u) | code;
 }
 
 /* Eight FP16 values (optionally minus eight FP16 reference values, the

@@ -60,7 +60,7 @@ __device__ __forceinline__ vec16 add_bias_vec(const vec16& x, const vec16& b) {
 }
 
 template <int FMT>
-__global__ void __launch_bounds__(kRopeThreads, 4)
+__global__ void __launch_bounds__(kRopeThreads, FMT == KV_RAW ? 4 : 3)
 rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
     __shared__ __align__(16) float cos_s[kRopeTableEntries];
     __shared__ __align__(16) float sin_s[kRopeTableEntries];

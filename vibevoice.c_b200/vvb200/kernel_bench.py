@@ -106,6 +106,17 @@ def run(peak_gbs: float, peak_kind: str):
         lambda b, s: ok(vv.vvb_rope_qk_append_dev(b[0], b[1], b[2], bq, bk, bv, b[3], b[4], rows, NQ, NKV, HD, 0, 0,
                                                   None, 1e6, 0, s)),
         rows * (NQ + 4 * NKV) * HD * 2, rows * (2 * NQ + 4 * NKV) * HD * 2, peak_gbs))
+    # the same launch for the FP8 (E4M3) KV cache: K and V leave as one byte per element, K minus a reference key
+    kref = rn(NKV * HD)
+    out.append(_case(
+        "rope_qk_append_fp8 [14449,28+4+4,128] with biases, e4m3 cache, reference key",
+        lambda: (rn(rows, NQ, HD), rn(rows, NKV, HD), rn(rows, NKV, HD),
+                 torch.empty(rows, NKV * HD, device=dev, dtype=torch.uint8),
+                 torch.empty(rows, NKV * HD, device=dev, dtype=torch.uint8)),
+        lambda b, s: ok(vv.vvb_rope_qk_append_fp8_dev(b[0], b[1], b[2], bq, bk, bv, b[3], b[4], kref, rows, NQ, NKV, HD,
+                                                      0, 0, None, 1e6, vv.VVB_KV_FP8_E4M3, 0, s)),
+        rows * (NQ + 2 * NKV) * HD * 2 + rows * 2 * NKV * HD, rows * (2 * NQ + 2 * NKV) * HD * 2 + rows * 2 * NKV * HD,
+        peak_gbs))
     # config 3: SwiGLU [4096,18944] and the decode shape [64,18944], in place on gate
     for rows in (4096, 64):
         out.append(_case(
