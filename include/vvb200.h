@@ -227,6 +227,7 @@ vv_status_t vvb_rope_qk_append_dev(void* q, void* k, const void* v,
 
 /** kv_format values of vvb_rope_qk_append_fp8_dev: numerically the reference's
  *  vv_kv_format_t (include/vibevoice/kv_quant.h:34-36). */
+#define VVB_KV_FP16     0
 #define VVB_KV_FP8_E4M3 1
 #define VVB_KV_FP8_E5M2 2
 
@@ -250,6 +251,39 @@ vv_status_t vvb_rope_qk_append_fp8_dev(void* q, void* k, const void* v,
                                        int rows, int n_q_heads, int n_kv_heads, int head_dim,
                                        int position_offset, int cache_offset, const int* d_position,
                                        float theta, int kv_format, int keep_k, void* stream);
+
+/** The general form of the two calls above, which also covers the PAGED cache
+ *  of the reference's server (contexts share one pool of 64-position pages,
+ *  include/vibevoice/kv_quant.h:47-53): logical position t = cache_offset + r
+ *  (or *d_position + r) is written to row page_table[t / 64] * 64 + t % 64 of
+ *  k_store / v_store, the mapping of src/cuda/kv_codec.cuh:29-36 that
+ *  vv_kv_store_dev applies (src/cuda/kv_quant.cu:508-551). page_table is a
+ *  device array with an entry for every page the call touches; NULL means a
+ *  contiguous cache (row t). kv_format: VVB_KV_FP16 (k_ref ignored),
+ *  VVB_KV_FP8_E4M3 or VVB_KV_FP8_E5M2. Everything else as documented for
+ *  vvb_rope_qk_append_dev and vvb_rope_qk_append_fp8_dev, which are this call
+ *  with page_table == NULL. */
+typedef struct vvb_kv_append {
+    void* q;                   /* [rows, n_q_heads, head_dim], rotated in place            */
+    void* k;                   /* [rows, n_kv_heads, head_dim], read (written if keep_k)   */
+    const void* v;             /* [rows, n_kv_heads, head_dim], read                       */
+    const void* q_bias;        /* [n_q_heads * head_dim] or NULL                           */
+    const void* k_bias;        /* [n_kv_heads * head_dim] or NULL                          */
+    const void* v_bias;        /* [n_kv_heads * head_dim] or NULL                          */
+    void* k_store;             /* one layer's K cache rows: FP16 or one byte per element   */
+    void* v_store;             /* one layer's V cache rows                                 */
+    const void* k_ref;         /* FP8 only: FP16 [n_kv_heads * head_dim] or NULL           */
+    const int* page_table;     /* device ints or NULL                                      */
+    const int* d_position;     /* device int or NULL                                       */
+    int rows, n_q_heads, n_kv_heads, head_dim;
+    int position_offset;       /* RoPE position of row 0 when d_position is NULL           */
+    int cache_offset;          /* logical cache position of row 0 when d_position is NULL  */
+    float theta;
+    int kv_format;
+    int keep_k;
+} vvb_kv_append_t;
+
+vv_status_t vvb_kv_append_dev(const vvb_kv_append_t* args, void* stream);
 
 /** Final RMSNorm + LM head + greedy argmax in two launches (the reference
  *  issues four: vv_rmsnorm_dev, vv_lm_head_gemv_dev and vv_argmax_dev's two,

@@ -185,6 +185,69 @@ def test_decode_by_device_position_under_graph_replay(vv, orc, fmt, name):
 
 
 @gpu
+@pytest.mark.parametrize("fmt", [0, 1, 2])
+def test_paged_cache_append(vv, orc, fmt):
+    """The server's paged cache (64-position pages of one pool): logical position t
+    lands in row page_table[t // 64] * 64 + t % 64 (src/cuda/kv_codec.cuh:29-36).
+    FP16 and both FP8 formats, against the oracle's contiguous result scattered by
+    the table, and against the reference's own vv_kv_store_dev where it is present."""
+    rng = np.random.default_rng(40 + fmt)
+    rows, first, pool_pages = 150, 70, 8
+    table = np.array([5, 2, 7, 0], np.int32)                 # pages of logical positions 0..255
+    q = rng.standard_normal((rows, NQ, HD)).astype(np.float16)
+    k = (rng.standard_normal((rows, NKV, HD)) * 1.5).astype(np.float16)
+    v = (rng.standard_normal((rows, NKV, HD)) * 0.05).astype(np.float16)
+    kb = (rng.standard_normal((NKV, HD)) * 0.3).astype(np.float16)
+    kref = (rng.standard_normal((NKV, HD)) * 0.5).astype(np.float16) if fmt else None
+    width = NKV * HD
+    kk = (k.astype(np.float32) + kb.astype(np.float32)).astype(np.float16)
+    dt, fill = (torch.uint8, 0xA5) if fmt else (torch.int16, 0x1234)
+    ks = torch.full((pool_pages * 64, width), fill, dtype=dt, device="cuda")
+    vs = torch.full((pool_pages * 64, width), fill, dtype=dt, device="cuda")
+    dk, dv, dtab = dev(k), dev(v), dev(table)
+    st = vv.vvb_kv_append_dev(dev(q), dk, dv, ks, vs, rows, NQ, NKV, HD, k_bias=dev(kb), k_ref=dev(kref) if fmt else None,
+                              page_table=dtab, position_offset=9, cache_offset=first, kv_format=fmt, keep_k=1)
+    assert st == 0, st
+    torch.cuda.synchronize()
+    # keep_k left the rotated FP16 K in place: it meets the RoPE bar against the oracle, and the
+    # cache must hold exactly that K (FP16) or exactly its FP8 bytes
+    k_rot = dk.cpu().numpy()
+    assert float(orc.rope_error_in_ulps(k_rot, orc.rope_f16(kk, 9, 1e6), kk).max()) <= 2.0
+    if fmt:
+        R = orc.restated()
+        want_k_rows, want_v_rows = R.kv_store_fp8(k_rot, kref, fmt), R.kv_store_fp8(v, None, fmt)
+    else:
+        want_k_rows, want_v_rows = k_rot.reshape(rows, width).view(np.uint16), v.reshape(rows, width).view(np.uint16)
+    np_dt = np.uint8 if fmt else np.uint16
+    want_k = np.full((pool_pages * 64, width), fill, np_dt)
+    want_v = np.full((pool_pages * 64, width), fill, np_dt)
+    for r in range(rows):
+        t = first + r
+        phys = int(table[t // 64]) * 64 + t % 64
+        want_k[phys], want_v[phys] = want_k_rows[r], want_v_rows[r]
+    got_k = ks.cpu().numpy().view(np_dt)
+    got_v = vs.cpu().numpy().view(np_dt)
+    bad_v = np.nonzero((got_v != want_v).any(axis=1))[0]
+    assert bad_v.size == 0, f"V rows differ: {bad_v[:8]}"
+    bad_k = np.nonzero((got_k != want_k).any(axis=1))[0]
+    assert bad_k.size == 0, f"K rows differ: {bad_k[:8]} ({int((got_k != want_k).sum())} elements)"
+
+    if os.path.exists(REF_CUDA):
+        ref = C.CDLL(REF_CUDA)
+        vp, i = C.c_void_p, C.c_int
+        ref.vv_kv_store_dev.argtypes = [vp, vp, vp, vp, vp, vp, vp, C.c_bool, i, i, i, vp, i, i, vp, vp]
+        ks2 = torch.full((pool_pages * 64, width), fill, dtype=dt, device="cuda")
+        vs2 = torch.full((pool_pages * 64, width), fill, dtype=dt, device="cuda")
+        dkref = dev(kref) if fmt else None
+        # dk holds the rotated FP16 K (keep_k): hand it to the reference's store
+        assert ref.vv_kv_store_dev(dk.data_ptr(), dv.data_ptr(), ks2.data_ptr(), vs2.data_ptr(), None, None,
+                                   dkref.data_ptr() if fmt else None, False, NKV, HD, first, None, rows, fmt,
+                                   dtab.data_ptr(), None) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(ks, ks2) and torch.equal(vs, vs2)
+
+
+@gpu
 def test_fp8_append_argument_checks(vv):
     z = torch.zeros(1, NKV, HD, dtype=torch.float16, device="cuda")
     zq = torch.zeros(1, NQ, HD, dtype=torch.float16, device="cuda")

@@ -51,15 +51,26 @@ struct RopeAppendArgs {
     const vec16* k_bias;
     const vec16* v_bias;
     const vec16* k_ref;       /* FP8 only: [n_kv_heads * head_dim] FP16 subtracted from K; may be null */
+    const int* page_table;    /* may be null: logical position t lives in cache row t */
     int cache_offset;         /* cache row of row 0 (when r.d_position is null) */
     int keep_k;               /* also write the rotated K back in place */
 };
+
+/* Cache row of logical position t. A paged cache (the server's slots share one
+ * pool of 64-position pages, include/vibevoice/kv_quant.h:47-53) maps page
+ * t / 64 through the context's table and keeps the offset inside the page
+ * (src/cuda/kv_codec.cuh:29-36). */
+constexpr int kKvPageShift = 6;
+__device__ __forceinline__ size_t cache_row(const int* page_table, int t) {
+    if (page_table == nullptr) return (size_t)t;
+    return ((size_t)__ldg(page_table + (t >> kKvPageShift)) << kKvPageShift) + (size_t)(t & ((1 << kKvPageShift) - 1));
+}
 
 __device__ __forceinline__ vec16 add_bias_vec(const vec16& x, const vec16& b) {
     return hadd8(x, b);      /* == widen, add, round to FP16 (vvb_device.cuh) */
 }
 
-template <int FMT>
+template <int FMT, bool PAGED>
 __global__ void __launch_bounds__(kRopeThreads, FMT == KV_RAW ? 4 : 3)
 rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
     __shared__ __align__(16) float cos_s[kRopeTableEntries];
@@ -83,7 +94,7 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
             const int cv = it - rl * cols_v;
             vec16 x = ld_stream(A.v + (size_t)(row0v + rl) * cols_v + cv);
             if (A.v_bias) x = add_bias_vec(x, __ldg(A.v_bias + cv));
-            const size_t at = (size_t)(cache_first_v + row0v + rl) * cols_v + cv;
+            const size_t at = cache_row(PAGED ? A.page_table : nullptr, cache_first_v + row0v + rl) * cols_v + cv;
             if (FMT == KV_RAW) st_stream(A.v_cache + at, x);
             else __stcs(reinterpret_cast<uint2*>(A.v_cache) + at, fp8_encode8<FMT>(x, nullptr));
         }
@@ -194,12 +205,14 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
         if (FMT != KV_RAW && to_cache) {
             /* one byte per element: vector i of the row is 8 bytes at uint2 index i */
             uint2* d8 = reinterpret_cast<uint2*>(A.k_cache) +
-                        ((size_t)(dst_row_first + row0 + rl) * stride + (size_t)(dst - A.k_cache));
+                        (cache_row(PAGED ? A.page_table : nullptr, dst_row_first + row0 + rl) * stride + (size_t)(dst - A.k_cache));
             const bool sub = A.k_ref != nullptr;
             __stcs(d8, fp8_encode8<FMT>(xlo, sub ? &rlo : nullptr));
             __stcs(d8 + a.hvn, fp8_encode8<FMT>(xhi, sub ? &rhi : nullptr));
         } else {
-            vec16* d = dst + (size_t)(dst_row_first + row0 + rl) * stride;
+            const size_t drow = to_cache ? cache_row(PAGED ? A.page_table : nullptr, dst_row_first + row0 + rl)
+                                         : (size_t)(row0 + rl);
+            vec16* d = dst + drow * stride;
             st_stream(d, xlo);
             st_stream(d + a.hvn, xhi);
         }
@@ -225,7 +238,7 @@ extern "C" int vvbk_rope_append(void* q, void* k, const void* v,
                                 int rows, int n_q_heads, int n_kv_heads, int head_dim,
                                 int position_offset, int cache_offset, const int* d_position,
                                 const float* inv_freq, int keep_k, int kv_format, const void* k_ref,
-                                void* stream) {
+                                const int* page_table, void* stream) {
     if (kv_format < KV_RAW || kv_format > KV_E5M2 || !aligned16(k_ref)) return (int)cudaErrorNotSupported;
     if (head_dim % 16 != 0 || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(q_bias) ||
         !aligned16(k_bias) || !aligned16(v_bias) || !aligned16(k_cache) || !aligned16(v_cache))
@@ -245,14 +258,22 @@ extern "C" int vvbk_rope_append(void* q, void* k, const void* v,
     A.k_bias = (const vec16*)k_bias;
     A.v_bias = (const vec16*)v_bias;
     A.k_ref = (kv_format == KV_RAW) ? nullptr : (const vec16*)k_ref;
+    A.page_table = page_table;
     A.cache_offset = cache_offset;
     A.keep_k = keep_k;
     if (gy > 65535u) return (int)cudaErrorInvalidValue;
     const dim3 grid(gx, gy), block(kRopeThreads);
     cudaStream_t s = (cudaStream_t)stream;
-    if (kv_format == KV_E4M3) launch_pdl(rope_append_kernel<KV_E4M3>, grid, block, 0, s, A);
-    else if (kv_format == KV_E5M2) launch_pdl(rope_append_kernel<KV_E5M2>, grid, block, 0, s, A);
-    else launch_pdl(rope_append_kernel<KV_RAW>, grid, block, 0, s, A);
+    /* the paged mapping is a template parameter so that the contiguous cache pays nothing for it */
+    if (page_table == nullptr) {
+        if (kv_format == KV_E4M3) launch_pdl(rope_append_kernel<KV_E4M3, false>, grid, block, 0, s, A);
+        else if (kv_format == KV_E5M2) launch_pdl(rope_append_kernel<KV_E5M2, false>, grid, block, 0, s, A);
+        else launch_pdl(rope_append_kernel<KV_RAW, false>, grid, block, 0, s, A);
+    } else {
+        if (kv_format == KV_E4M3) launch_pdl(rope_append_kernel<KV_E4M3, true>, grid, block, 0, s, A);
+        else if (kv_format == KV_E5M2) launch_pdl(rope_append_kernel<KV_E5M2, true>, grid, block, 0, s, A);
+        else launch_pdl(rope_append_kernel<KV_RAW, true>, grid, block, 0, s, A);
+    }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }

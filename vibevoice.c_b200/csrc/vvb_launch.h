@@ -37,14 +37,16 @@ int vvbk_rope(void* q, void* k, int rows, int n_q_heads, int n_kv_heads, int hea
  * Returns cudaErrorNotSupported (801) without launching when head_dim % 16 != 0
  * or a pointer is not 16-byte aligned. kv_format: 0 raw FP16 cache, 1 / 2 the
  * reference's software FP8 E4M3 / E5M2 bytes (one per element); k_ref (FP8
- * only, may be null): FP16 [n_kv_heads * head_dim] subtracted from K first. */
+ * only, may be null): FP16 [n_kv_heads * head_dim] subtracted from K first.
+ * page_table (may be null): device ints, one per 64-position page of the
+ * logical sequence, giving the page's index in the cache arrays. */
 int vvbk_rope_append(void* q, void* k, const void* v,
                      const void* q_bias, const void* k_bias, const void* v_bias,
                      void* k_cache, void* v_cache,
                      int rows, int n_q_heads, int n_kv_heads, int head_dim,
                      int position_offset, int cache_offset, const int* d_position,
                      const float* inv_freq, int keep_k, int kv_format, const void* k_ref,
-                     void* stream);
+                     const int* page_table, void* stream);
 
 /* SwiGLU (csrc/swiglu.cu). Flat: gate/up/out of n elements. Fused: rows of
  * [gate | up] with 2*inter halves per row. */

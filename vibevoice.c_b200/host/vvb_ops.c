@@ -63,24 +63,39 @@ vv_status_t vvb_rope_qk_dev(void* q, void* k, int rows, int n_q_heads, int n_kv_
                                position_offset, d_position, inv_freq, stream));
 }
 
+vv_status_t vvb_kv_append_dev(const vvb_kv_append_t* a, void* stream) {
+    if (!a) return VV_ERR_NULL_PTR;
+    if (!a->q || !a->k || !a->v || !a->k_store || !a->v_store) return VV_ERR_NULL_PTR;
+    if (a->rows < 0 || a->n_q_heads <= 0 || a->n_kv_heads <= 0 || a->head_dim <= 0 || a->cache_offset < 0)
+        return VV_ERR_INVALID_ARG;
+    /* the reference's vv_kv_format_t: 0 FP16, 1 FP8 E4M3, 2 FP8 E5M2 (its own
+     * FP8 store takes head_dim 128 only, src/cuda/kv_quant.cu:527; the byte
+     * layout is defined for any head_dim and this kernel takes multiples of
+     * 16). The TurboQuant formats (3..6) are not written by this library. */
+    if (a->kv_format != VVB_KV_FP16 && a->kv_format != VVB_KV_FP8_E4M3 && a->kv_format != VVB_KV_FP8_E5M2)
+        return VV_ERR_UNSUPPORTED;
+    if (a->rows == 0) return VV_OK;
+    if (a->head_dim / 2 > VVB_ROPE_MAX_HALF) return VV_ERR_UNSUPPORTED;
+    float inv_freq[VVB_ROPE_MAX_HALF];
+    fill_inv_freq(inv_freq, a->head_dim, a->theta);
+    const int err = vvbk_rope_append(a->q, a->k, a->v, a->q_bias, a->k_bias, a->v_bias, a->k_store, a->v_store,
+                                     a->rows, a->n_q_heads, a->n_kv_heads, a->head_dim, a->position_offset,
+                                     a->cache_offset, a->d_position, inv_freq, a->keep_k, a->kv_format,
+                                     a->kv_format == VVB_KV_FP16 ? NULL : a->k_ref, a->page_table, stream);
+    if (err == 801) return VV_ERR_UNSUPPORTED;   /* cudaErrorNotSupported: not vectorisable */
+    return from_cuda(err);
+}
+
 static vv_status_t rope_qk_append(void* q, void* k, const void* v,
                                   const void* q_bias, const void* k_bias, const void* v_bias,
                                   void* k_cache, void* v_cache, const void* k_ref,
                                   int rows, int n_q_heads, int n_kv_heads, int head_dim,
                                   int position_offset, int cache_offset, const int* d_position,
                                   float theta, int kv_format, int keep_k, void* stream) {
-    if (!q || !k || !v || !k_cache || !v_cache) return VV_ERR_NULL_PTR;
-    if (rows < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || cache_offset < 0)
-        return VV_ERR_INVALID_ARG;
-    if (rows == 0) return VV_OK;
-    if (head_dim / 2 > VVB_ROPE_MAX_HALF) return VV_ERR_UNSUPPORTED;
-    float inv_freq[VVB_ROPE_MAX_HALF];
-    fill_inv_freq(inv_freq, head_dim, theta);
-    const int err = vvbk_rope_append(q, k, v, q_bias, k_bias, v_bias, k_cache, v_cache, rows,
-                                     n_q_heads, n_kv_heads, head_dim, position_offset, cache_offset,
-                                     d_position, inv_freq, keep_k, kv_format, k_ref, stream);
-    if (err == 801) return VV_ERR_UNSUPPORTED;   /* cudaErrorNotSupported: not vectorisable */
-    return from_cuda(err);
+    const vvb_kv_append_t a = {q, k, v, q_bias, k_bias, v_bias, k_cache, v_cache, k_ref, NULL, d_position,
+                               rows, n_q_heads, n_kv_heads, head_dim, position_offset, cache_offset,
+                               theta, kv_format, keep_k};
+    return vvb_kv_append_dev(&a, stream);
 }
 
 vv_status_t vvb_rope_qk_append_dev(void* q, void* k, const void* v,

@@ -59,8 +59,19 @@ class LayerChain(C.Structure):
     ]
 
 
+class KvAppend(C.Structure):
+    """vvb_kv_append_t (include/vvb200.h)."""
+    _fields_ = [
+        ("q", _vp), ("k", _vp), ("v", _vp), ("q_bias", _vp), ("k_bias", _vp), ("v_bias", _vp),
+        ("k_store", _vp), ("v_store", _vp), ("k_ref", _vp), ("page_table", _vp), ("d_position", _vp),
+        ("rows", _i), ("n_q_heads", _i), ("n_kv_heads", _i), ("head_dim", _i),
+        ("position_offset", _i), ("cache_offset", _i), ("theta", _f), ("kv_format", _i), ("keep_k", _i),
+    ]
+
+
 # name -> (restype, argtypes): every symbol include/vvb200.h declares
 SIGNATURES = {
+    "vvb_kv_append_dev": (_i, [C.POINTER(KvAppend), _vp]),
     "vv_embedding_dev": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "vv_rmsnorm_dev": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp]),
     "vv_rope_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _f, _vp]),
@@ -257,7 +268,17 @@ def vvb_rope_qk_append_dev(q, k, v, q_bias, k_bias, v_bias, k_cache, v_cache, ro
                                        _stream(stream))
 
 
-VVB_KV_FP8_E4M3, VVB_KV_FP8_E5M2 = 1, 2
+VVB_KV_FP16, VVB_KV_FP8_E4M3, VVB_KV_FP8_E5M2 = 0, 1, 2
+
+
+def vvb_kv_append_dev(q, k, v, k_store, v_store, rows, n_q_heads, n_kv_heads, head_dim, *, q_bias=None, k_bias=None,
+                      v_bias=None, k_ref=None, page_table=None, d_position=None, position_offset=0, cache_offset=0,
+                      theta=1e6, kv_format=0, keep_k=0, stream=None) -> int:
+    """Bias adds + RoPE + KV-cache append (FP16 or FP8, contiguous or paged) in one launch."""
+    a = KvAppend(_ptr(q), _ptr(k), _ptr(v), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias), _ptr(k_store), _ptr(v_store),
+                 _ptr(k_ref), _ptr(page_table), _ptr(d_position), rows, n_q_heads, n_kv_heads, head_dim,
+                 position_offset, cache_offset, theta, kv_format, keep_k)
+    return _lib.vvb_kv_append_dev(C.byref(a), _stream(stream))
 
 
 def vvb_rope_qk_append_fp8_dev(q, k, v, q_bias, k_bias, v_bias, k_store, v_store, k_ref, rows, n_q_heads,
