@@ -80,7 +80,7 @@ def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def expected(orc, q, k, v, qb, kb, vb, kref, pos0, row0, max_len, fmt, theta=1e6):
+def expected(orc, q, k, v, qb, kb, vb, kref, pos0, row0, max_len, fmt, theta=1e6, NKV=NKV, HD=HD):
     """The reference's sequence on the CPU: bias adds rounded to FP16, RoPE, FP16
     result, then the FP8 store (K minus the reference key, V as is)."""
     add = lambda x, b: (x.astype(np.float32) + b.astype(np.float32)).astype(np.float16) if b is not None else x
@@ -127,6 +127,37 @@ def test_fused_fp8_append_equals_oracle(vv, orc, fmt, name, rows, with_bias, wit
         assert np.array_equal(got_k.view(np.uint16), k.view(np.uint16))       # K itself untouched
     # V is never modified
     assert np.array_equal(dv.cpu().numpy().view(np.uint16), v.view(np.uint16))
+
+
+@gpu
+@pytest.mark.parametrize("fmt", [1, 2])
+@pytest.mark.parametrize("rows,nq,nkv,hd", [(9, 8, 40, 128),      # many KV heads: K tile too large to stage
+                                            (75, 4, 2, 64),       # narrow heads: 10 rows per pass, staged
+                                            (33, 2, 1, 256)])     # wide head
+def test_fused_fp8_append_other_shapes(vv, orc, fmt, rows, nq, nkv, hd):
+    rng = np.random.default_rng(rows * 7 + fmt)
+    q = rng.standard_normal((rows, nq, hd)).astype(np.float16)
+    k = (rng.standard_normal((rows, nkv, hd)) * 1.5).astype(np.float16)
+    v = (rng.standard_normal((rows, nkv, hd)) * 0.05).astype(np.float16)
+    kb = (rng.standard_normal((nkv, hd)) * 0.3).astype(np.float16)
+    kref = (rng.standard_normal((nkv, hd)) * 0.5).astype(np.float16)
+    pos0, row0, max_len = 77, 3, rows + 5
+    want_q, want_k, want_ks, want_vs = expected(orc, q, k, v, None, kb, None, kref, pos0, row0, max_len, fmt, NKV=nkv, HD=hd)
+    dq, dk, dv = dev(q), dev(k), dev(v)
+    ks = torch.full((max_len, nkv * hd), 0xA5, dtype=torch.uint8, device="cuda")
+    vs = torch.full((max_len, nkv * hd), 0xA5, dtype=torch.uint8, device="cuda")
+    st = vv.vvb_rope_qk_append_fp8_dev(dq, dk, dv, None, dev(kb), None, ks, vs, dev(kref), rows, nq, nkv, hd,
+                                       pos0, row0, None, 1e6, fmt, 1)
+    assert st == 0, st
+    torch.cuda.synchronize()
+    # the cache holds the bytes of the K this launch rotated (kept in place), and that K meets the RoPE bar
+    kk = (k.astype(np.float32) + kb.astype(np.float32)).astype(np.float16)
+    k_rot = dk.cpu().numpy()
+    assert float(orc.rope_error_in_ulps(k_rot, want_k, kk).max()) <= 2.0
+    R = orc.restated()
+    assert np.array_equal(ks.cpu().numpy(), R.kv_store_fp8(k_rot, kref, fmt, row0, np.full((max_len, nkv * hd), 0xA5, np.uint8)))
+    assert np.array_equal(vs.cpu().numpy(), want_vs)
+    assert float(orc.rope_error_in_ulps(dq.cpu().numpy(), want_q, q).max()) <= 2.0
 
 
 @gpu

@@ -6,7 +6,7 @@
  * (src/inference/decoder.c:463-464 vv_bias_add_dev on q, k, v; :850-855
  * vv_rope_dev on Q then K; src/inference/kv_cache.c:229-246 two device copies
  * of K and V into the layer's cache). Here one grid carries RoPE tiles
- * (rope.cuh) over the Q and K columns and, in its last grid row, flat copy CTAs
+ * (rope.cuh) over the Q and K columns and, in its first grid row, flat copy CTAs
  * for V:
  *   Q head   x = f16(q + bias_q), rotate, store in place
  *   K head   x = f16(k + bias_k), rotate, store INTO THE CACHE row
@@ -80,26 +80,42 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
     pdl_wait();
     pdl_trigger();
 
-    /* The last grid row (blockIdx.y) carries V: no rotation, so no table and
-     * no barrier -- a flat copy (+ bias) of kVRowsPerCta rows per CTA into the
-     * cache. Fewer CTAs are needed than the grid has columns; the rest exit. */
-    if (blockIdx.y == gridDim.y - 1) {
+    /* The FIRST grid row (blockIdx.y == 0) carries V: no rotation, so no table
+     * and no barrier -- a flat copy (+ bias, + FP8 encoding) of kVRowsPerCta
+     * rows per CTA into the cache. Fewer CTAs are needed than the grid has
+     * columns; the rest exit. These CTAs are the longest of the grid (each
+     * walks 32 rows), so they are dispatched first and the short RoPE tiles
+     * fill in behind them instead of waiting for a tail of V copies; four
+     * loads per thread are in flight at a time. */
+    if (blockIdx.y == 0) {
         const int cols_v = a.n_kv * 2 * a.hvn;                 /* vectors per V row */
         const int row0v = blockIdx.x * kVRowsPerCta;
         if (row0v >= a.rows) return;
-        const int nrows_v = min(kVRowsPerCta, a.rows - row0v);
+        const int items = min(kVRowsPerCta, a.rows - row0v) * cols_v;
         const int cache_first_v = (a.d_position != nullptr) ? *a.d_position : A.cache_offset;
-        for (int it = t; it < nrows_v * cols_v; it += kRopeThreads) {
-            const int rl = it / cols_v;
-            const int cv = it - rl * cols_v;
-            vec16 x = ld_stream(A.v + (size_t)(row0v + rl) * cols_v + cv);
-            if (A.v_bias) x = add_bias_vec(x, __ldg(A.v_bias + cv));
-            const size_t at = cache_row(PAGED ? A.page_table : nullptr, cache_first_v + row0v + rl) * cols_v + cv;
-            if (FMT == KV_RAW) st_stream(A.v_cache + at, x);
-            else __stcs(reinterpret_cast<uint2*>(A.v_cache) + at, fp8_encode8<FMT>(x, nullptr));
+        constexpr int kVUnroll = 4;
+        for (int base = t; base < items; base += kRopeThreads * kVUnroll) {
+            vec16 x[kVUnroll];
+#pragma unroll
+            for (int j = 0; j < kVUnroll; j++) {
+                const int it = base + j * kRopeThreads;
+                if (it < items) x[j] = ld_stream(A.v + (size_t)row0v * cols_v + it);
+            }
+#pragma unroll
+            for (int j = 0; j < kVUnroll; j++) {
+                const int it = base + j * kRopeThreads;
+                if (it >= items) continue;
+                const int rl = it / cols_v;
+                const int cv = it - rl * cols_v;
+                if (A.v_bias) x[j] = add_bias_vec(x[j], __ldg(A.v_bias + cv));
+                const size_t at = cache_row(PAGED ? A.page_table : nullptr, cache_first_v + row0v + rl) * cols_v + cv;
+                if (FMT == KV_RAW) st_stream(A.v_cache + at, x[j]);
+                else __stcs(reinterpret_cast<uint2*>(A.v_cache) + at, fp8_encode8<FMT>(x[j], nullptr));
+            }
         }
         return;
     }
+    const int by = (int)blockIdx.y - 1;                        /* column chunk of this RoPE tile */
 
     const int rows_per_cta = a.row_slots * a.passes;
     const int row0 = blockIdx.x * rows_per_cta;
@@ -108,7 +124,7 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
     /* This thread's column (tensor, head, vector), fixed for all its rows. */
     const int slot = t / a.cols_per_cta;
     const int cl = t - slot * a.cols_per_cta;
-    const int c = blockIdx.y * kRopeThreads + cl;
+    const int c = by * kRopeThreads + cl;
     const bool col_ok = (slot < a.row_slots) && (c < a.items_per_row);
     const int head = c / a.hvn;
     const int vec = c - head * a.hvn;
@@ -116,6 +132,16 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
     const int dev_pos = (a.d_position != nullptr) ? *a.d_position : 0;
     const int pos_first = (a.d_position != nullptr) ? dev_pos : a.position_offset;
     const int cache_first = (a.d_position != nullptr) ? dev_pos : A.cache_offset;
+
+    /* FP8: the K columns of this CTA's column chunk are staged through shared
+     * memory (phase D) when the tile fits: 4 rows x 4 heads of 128 are 256 vectors. */
+    constexpr int kStageVecs = 512;
+    __shared__ vec16 k_stage[FMT == KV_RAW ? 1 : kStageVecs];
+    const int chunk0 = by * kRopeThreads;
+    const int chunk1 = min(chunk0 + a.cols_per_cta, a.items_per_row);
+    const int first_k_col = max(chunk0, a.n_q * a.hvn);
+    const int kcols = max(0, chunk1 - first_k_col);
+    const bool staged = (FMT != KV_RAW) && kcols > 0 && kcols * 2 * rows_per_cta <= kStageVecs;
 
     const vec16* src;
     vec16* dst;
@@ -138,7 +164,7 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
         dst = A.k_cache + off;
         dst_row_first = cache_first;
         to_cache = true;
-        if (FMT != KV_RAW && A.k_ref != nullptr && col_ok) {
+        if (FMT != KV_RAW && A.k_ref != nullptr && col_ok && !staged) {
             rlo = __ldg(A.k_ref + off);
             rhi = __ldg(A.k_ref + off + a.hvn);
         }
@@ -202,7 +228,11 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
             xlo = pack8(y0);
             xhi = pack8(y1);
         }
-        if (FMT != KV_RAW && to_cache) {
+        if (FMT != KV_RAW && to_cache && staged) {
+            /* hand the rotated FP16 K to the whole CTA for encoding (phase D) */
+            k_stage[(rl * 2 + 0) * kcols + (c - first_k_col)] = xlo;
+            k_stage[(rl * 2 + 1) * kcols + (c - first_k_col)] = xhi;
+        } else if (FMT != KV_RAW && to_cache) {
             /* one byte per element: vector i of the row is 8 bytes at uint2 index i */
             uint2* d8 = reinterpret_cast<uint2*>(A.k_cache) +
                         (cache_row(PAGED ? A.page_table : nullptr, dst_row_first + row0 + rl) * stride + (size_t)(dst - A.k_cache));
@@ -220,6 +250,33 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
             vec16* d2 = dst_keep + (size_t)(row0 + rl) * stride;
             st_stream(d2, xlo);
             st_stream(d2 + a.hvn, xhi);
+        }
+    }
+
+    /* Phase D (FP8): the encoder costs several times the rotation, and the K
+     * columns of a CTA sit in few of its warps (one of eight for the 7B shape),
+     * which would finish long after the others. The staged K tile is therefore
+     * encoded by ALL threads, one 16-byte vector (8 bytes out) at a time;
+     * consecutive threads write consecutive 8-byte pieces of a cache row. */
+    if (FMT != KV_RAW && staged) {
+        __syncthreads();
+        const size_t stride_k = (size_t)a.n_kv * vph;
+        for (int idx = t; idx < nrows * 2 * kcols; idx += kRopeThreads) {
+            const int rh = idx / kcols;                    /* (row, half) */
+            const int kc = idx - rh * kcols;
+            const int rl = rh >> 1;
+            const int ck = first_k_col + kc;
+            const int hd = ck / a.hvn;
+            const size_t off = (size_t)(hd - a.n_q) * vph + (size_t)(ck - hd * a.hvn) + ((rh & 1) ? (size_t)a.hvn : 0);
+            uint2* d8 = reinterpret_cast<uint2*>(A.k_cache) +
+                        (cache_row(PAGED ? A.page_table : nullptr, cache_first + row0 + rl) * stride_k + off);
+            const vec16 x = k_stage[idx];
+            if (A.k_ref != nullptr) {
+                const vec16 r = __ldg(A.k_ref + off);
+                __stcs(d8, fp8_encode8<FMT>(x, &r));
+            } else {
+                __stcs(d8, fp8_encode8<FMT>(x, nullptr));
+            }
         }
     }
 }
@@ -245,7 +302,7 @@ extern "C" int vvbk_rope_append(void* q, void* k, const void* v,
         return (int)cudaErrorNotSupported;
     RopeAppendArgs A;
     unsigned gx, gy;
-    /* tiles over the Q and K heads; one more grid row (the last) carries V */
+    /* tiles over the Q and K heads; one more grid row (the first) carries V */
     rope_plan(A.r, q, k, rows, n_q_heads, n_kv_heads, head_dim, position_offset, d_position, inv_freq,
               kRopeMaxRowsPerThread, &gx, &gy);
     const unsigned gx_v = (unsigned)((rows + kVRowsPerCta - 1) / kVRowsPerCta);
