@@ -132,6 +132,20 @@ def test_argument_validation_needs_no_gpu(vv):
     assert vv.vvb_embedding_rmsnorm_dev(P, P, P, None, P, 1, 8, 10, 1e-6, stream=0) == vv.VV_ERR_NULL_PTR
     assert vv._lib.vvb_layer_chain_dev(None, 0) == vv.VV_ERR_NULL_PTR
     assert vv._lib.vvb_layer_chain_host(None, None) == vv.VV_ERR_NULL_PTR
+    # the fused KV-cache append, in its three forms
+    assert vv._lib.vvb_kv_append_dev(None, 0) == vv.VV_ERR_NULL_PTR
+    kv = lambda **kw: vv.vvb_kv_append_dev(kw.pop("q", P), kw.pop("k", P), P, kw.pop("ks", P), P, kw.pop("rows", 1),
+                                           28, 4, 128, stream=0, **kw)
+    assert kv(q=None) == vv.VV_ERR_NULL_PTR and kv(k=None) == vv.VV_ERR_NULL_PTR and kv(ks=None) == vv.VV_ERR_NULL_PTR
+    assert kv(rows=-1) == vv.VV_ERR_INVALID_ARG and kv(cache_offset=-1) == vv.VV_ERR_INVALID_ARG
+    assert kv(kv_format=3) == vv.VV_ERR_UNSUPPORTED and kv(kv_format=-1) == vv.VV_ERR_UNSUPPORTED   # TurboQuant: not here
+    assert kv(rows=0) == vv.VV_OK and kv(rows=0, kv_format=2, page_table=P) == vv.VV_OK
+    assert vv.vvb_rope_qk_append_dev(P, P, None, None, None, None, P, P, 1, 28, 4, 128, 0, 0, None, 1e6, 0, 0) \
+        == vv.VV_ERR_NULL_PTR
+    assert vv.vvb_rope_qk_append_fp8_dev(P, P, P, None, None, None, P, P, None, 1, 28, 4, 128, 0, 0, None, 1e6, 0, 0, 0) \
+        == vv.VV_ERR_UNSUPPORTED                                     # kv_format 0 is the FP16 cache: the other call
+    assert vv.vvb_rope_qk_append_fp8_dev(P, P, P, None, None, None, P, P, None, 0, 28, 4, 128, 0, 0, None, 1e6, 1, 0, 0) \
+        == vv.VV_OK
     ctx = C.c_void_p()
     assert vv._lib.vvb_host_ctx_create(C.byref(ctx), 0, 0, 8, 1, 1, 16, 8) == vv.VV_ERR_INVALID_ARG
     assert vv._lib.vvb_host_ctx_create(None, 0, 1, 8, 1, 1, 16, 8) == vv.VV_ERR_NULL_PTR

@@ -24,6 +24,8 @@
 #pragma once
 #include "vvb_device.cuh"
 
+#include <cuda_fp8.h>
+
 namespace vvb {
 
 enum { KV_RAW = 0, KV_E4M3 = 1, KV_E5M2 = 2 };
@@ -69,6 +71,37 @@ __device__ __forceinline__ uint2 fp8_encode8(const vec16& x, const vec16* ref) {
 #pragma unroll
         for (int e = 0; e < 8; e++) f[e] = __fsub_rn(f[e], r[e]);
     }
+#ifdef VVB_FP8_HW
+    /* The hardware conversion (cvt.rn.satfinite to e4m3x2 / e5m2x2) agrees
+     * with the mapping above except in two places, both repaired here:
+     *  - below the smallest normal it rounds ties to even where the reference
+     *    rounds them up. Scaling such a value by 1 + 2^-19 first moves every
+     *    exact tie above its half-way point and nothing else across one: ties
+     *    are odd multiples of 2^-10 (2^-17 for E5M2), the inputs lie on the
+     *    FP16 grid or are differences of two FP16 values, so the nearest input
+     *    below a tie is at least 2^-24 away, and the scaling moves a value
+     *    below 2^-6 by less than 2^-25;
+     *  - it stores NaN as NaN; the reference stores zero. */
+    constexpr uint32_t MIN_NORMAL = (uint32_t)(127 + 1 - ((FMT == KV_E4M3) ? 7 : 15)) << 23;
+    constexpr uint32_t NAN_ADD = (FMT == KV_E4M3) ? 0x01010101u : 0x04040404u;   /* 0x80 - (largest finite code + 1) */
+    const float nudge = 1.0f + 1.9073486328125e-06f;                             /* 1 + 2^-19 */
+    uint32_t w[4];
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+        float a0 = f[2 * p], a1 = f[2 * p + 1];
+        if ((__float_as_uint(a0) & 0x7fffffffu) < MIN_NORMAL) a0 = __fmul_rn(a0, nudge);
+        if ((__float_as_uint(a1) & 0x7fffffffu) < MIN_NORMAL) a1 = __fmul_rn(a1, nudge);
+        w[p] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(a0, a1), __NV_SATFINITE,
+                                                  (FMT == KV_E4M3) ? __NV_E4M3 : __NV_E5M2);
+    }
+    uint32_t lo = w[0] | (w[1] << 16), hi = w[2] | (w[3] << 16);
+    /* a byte whose low seven bits exceed the largest finite code is a NaN: clear it */
+    const uint32_t nlo = (((lo & 0x7f7f7f7fu) + NAN_ADD) & 0x80808080u) >> 7;
+    const uint32_t nhi = (((hi & 0x7f7f7f7fu) + NAN_ADD) & 0x80808080u) >> 7;
+    lo &= ~(nlo * 0xFFu);
+    hi &= ~(nhi * 0xFFu);
+    return make_uint2(lo, hi);
+#else
     uint32_t lo = 0, hi = 0;
 #pragma unroll
     for (int e = 0; e < 4; e++) {
@@ -76,6 +109,7 @@ __device__ __forceinline__ uint2 fp8_encode8(const vec16& x, const vec16* ref) {
         hi |= fp8_encode<FMT>(f[e + 4]) << (8 * e);
     }
     return make_uint2(lo, hi);
+#endif
 }
 
 }  // namespace vvb
