@@ -277,6 +277,28 @@ def test_paged_cache_append(vv, orc, fmt):
         torch.cuda.synchronize()
         assert torch.equal(ks, ks2) and torch.equal(vs, vs2)
 
+    # a decode step on the same paged cache: the device int gives the RoPE position AND the
+    # logical cache position, which the page table maps (position 220 -> page 3 -> pool page 0)
+    pos = first + rows
+    dpos = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    k1 = (rng.standard_normal((1, NKV, HD)) * 1.5).astype(np.float16)
+    v1 = (rng.standard_normal((1, NKV, HD)) * 0.05).astype(np.float16)
+    dk1 = dev(k1)
+    before_k, before_v = ks.clone(), vs.clone()
+    assert vv.vvb_kv_append_dev(dev(q[:1]), dk1, dev(v1), ks, vs, 1, NQ, NKV, HD, k_ref=dev(kref) if fmt else None,
+                                page_table=dtab, d_position=dpos, kv_format=fmt, keep_k=1) == 0
+    torch.cuda.synchronize()
+    phys = int(table[pos // 64]) * 64 + pos % 64
+    k1_rot = dk1.cpu().numpy()
+    assert float(orc.rope_error_in_ulps(k1_rot, orc.rope_f16(k1, pos, 1e6), k1).max()) <= 2.0
+    if fmt:
+        wk, wv = R.kv_store_fp8(k1_rot, kref, fmt)[0], R.kv_store_fp8(v1, None, fmt)[0]
+    else:
+        wk, wv = k1_rot.reshape(width).view(np.uint16), v1.reshape(width).view(np.uint16)
+    assert np.array_equal(ks[phys].cpu().numpy().view(np_dt), wk) and np.array_equal(vs[phys].cpu().numpy().view(np_dt), wv)
+    before_k[phys], before_v[phys] = ks[phys], vs[phys]
+    assert torch.equal(before_k, ks) and torch.equal(before_v, vs)        # no other row moved
+
 
 @gpu
 def test_fp8_append_argument_checks(vv):

@@ -52,6 +52,17 @@ __device__ __forceinline__ int q8_pos(int layout, int j) {
     return j;
 }
 
+/* 4 x 4 byte transpose across four consecutive lanes: lane i (0..3) gives the
+ * word [v_i.b0 .. v_i.b3] and receives [v_0.b_i, v_1.b_i, v_2.b_i, v_3.b_i].
+ * Two butterfly steps (halves with lane ^ 2, bytes with lane ^ 1); every lane
+ * of the warp must call it. */
+__device__ __forceinline__ uint32_t transpose4(uint32_t v, int i) {
+    const uint32_t x = __shfl_xor_sync(0xffffffffu, v, 2);
+    v = (i & 2) ? __byte_perm(x, v, 0x7632) : __byte_perm(v, x, 0x5410);
+    const uint32_t y = __shfl_xor_sync(0xffffffffu, v, 1);
+    return (i & 1) ? __byte_perm(y, v, 0x7351) : __byte_perm(v, y, 0x6240);
+}
+
 template <int VPT, int MODE>
 __global__ void __launch_bounds__(1024)
 act_quant_kernel(const ActQuantArgs a) {
@@ -135,6 +146,27 @@ act_quant_kernel(const ActQuantArgs a) {
         const uint32_t lo = __byte_perm(__byte_perm(rb[0], rb[1], 0x0040), __byte_perm(rb[2], rb[3], 0x0040), 0x5410);
         const uint32_t hi = __byte_perm(__byte_perm(rb[4], rb[5], 0x0040), __byte_perm(rb[6], rb[7], 0x0040), 0x5410);
         int s = __dp4a((int)lo, 0x01010101, __dp4a((int)hi, 0x01010101, 0));   /* sum of the 8 signed bytes */
+        /* The two weight-GEMM layouts interleave the bytes of the four threads
+         * that share a run: the bytes are exchanged with shuffles so that every
+         * thread stores two whole 32-bit words instead of eight single bytes.
+         * (All four threads of a run are in range together: nvec % 4 == 0.) */
+        uint32_t w0 = 0, w1 = 0;
+        int o0 = 0;
+        if (a.layout == 3) {
+            /* byte position 16*odd + 4*word + i: word w of the run's first half
+             * is column 2w of the four chunks, of its second half column 2w+1 */
+            w0 = transpose4(__byte_perm(lo, hi, 0x6420), t & 3);
+            w1 = transpose4(__byte_perm(lo, hi, 0x7531), t & 3);
+        } else if (a.layout == 2) {
+            /* word 2w + (i & 1) = [chunk i&1: col 2w, chunk (i&1)+2: col 2w, then both again for
+             * col 2w+1]: threads i and i^2 swap halves and each builds two words */
+            const bool high = (t & 2) != 0;
+            const uint32_t x = __shfl_xor_sync(0xffffffffu, high ? lo : hi, 2);
+            const uint32_t first = high ? x : lo, second = high ? hi : x;
+            w0 = __byte_perm(first, second, 0x5140);
+            w1 = __byte_perm(first, second, 0x7362);
+            o0 = (high ? 16 : 0) + 4 * (t & 1);
+        }
         if (ok) {
             int8_t* run = xq + ((size_t)(v >> 2) << 5);
             const int i = v & 3;
@@ -144,12 +176,12 @@ act_quant_kernel(const ActQuantArgs a) {
                 /* evens of the chunk at 4i.., odds at 16 + 4i.. */
                 *reinterpret_cast<uint32_t*>(run + (i << 2)) = __byte_perm(lo, hi, 0x6420);
                 *reinterpret_cast<uint32_t*>(run + 16 + (i << 2)) = __byte_perm(lo, hi, 0x7531);
+            } else if (a.layout == 3) {
+                *reinterpret_cast<uint32_t*>(run + (i << 2)) = w0;
+                *reinterpret_cast<uint32_t*>(run + 16 + (i << 2)) = w1;
             } else {
-#pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    const uint32_t w = e < 4 ? lo : hi;
-                    run[q8_pos(a.layout, (i << 3) + e)] = (int8_t)(w >> (8 * (e & 3)));
-                }
+                *reinterpret_cast<uint32_t*>(run + o0) = w0;
+                *reinterpret_cast<uint32_t*>(run + o0 + 8) = w1;
             }
         }
         if (xsum != nullptr) {
