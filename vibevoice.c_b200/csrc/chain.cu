@@ -31,6 +31,13 @@ constexpr int kChainNormGroup = 128;     /* threads per row */
 constexpr int kChainNormVPT = 4;         /* => hidden <= 128 * 4 * 8 = 4096 */
 constexpr int kChainSwigluUnroll = 4;
 
+/* CTAs per SM the kernel is compiled for. At 4 the register cap is 64 and the
+ * kernel spills a few words (328.6 us per step at 14449 rows); at 3 it takes 75
+ * registers, spills nothing and runs 326.0 us (45.1 us at 1807 rows either way). */
+#ifndef VVB_CHAIN_CTAS
+#define VVB_CHAIN_CTAS 3
+#endif
+
 struct ChainArgs {
     RowNormArgs norm;
     RopeArgs rope;
@@ -41,7 +48,7 @@ struct ChainArgs {
     unsigned norm_ctas, rope_gx, rope_ctas;
 };
 
-__global__ void __launch_bounds__(kChainThreads, 4)
+__global__ void __launch_bounds__(kChainThreads, VVB_CHAIN_CTAS)
 layer_chain_kernel(const __grid_constant__ ChainArgs a) {
     pdl_wait();
     pdl_trigger();

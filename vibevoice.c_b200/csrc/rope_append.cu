@@ -42,6 +42,13 @@ extern std::atomic<uint64_t> g_launches;
 
 constexpr int kVRowsPerCta = 32;
 
+/* CTAs per SM the FP16 variant is compiled for (the FP8 variants take 3: at 4
+ * they spill and run 61.7 instead of 48.0 us; the FP16 variant measures 43.8 us
+ * at 3 without spills against 44.3 at 4 with 124 bytes of spill loads). */
+#ifndef VVB_ROPE_APPEND_RAW_CTAS
+#define VVB_ROPE_APPEND_RAW_CTAS 3
+#endif
+
 struct RopeAppendArgs {
     RopeArgs r;               /* tile plan over the n_q + n_kv rotated heads */
     const vec16* v;
@@ -71,7 +78,7 @@ __device__ __forceinline__ vec16 add_bias_vec(const vec16& x, const vec16& b) {
 }
 
 template <int FMT, bool PAGED>
-__global__ void __launch_bounds__(kRopeThreads, FMT == KV_RAW ? 4 : 3)
+__global__ void __launch_bounds__(kRopeThreads, FMT == KV_RAW ? VVB_ROPE_APPEND_RAW_CTAS : 3)
 rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
     __shared__ __align__(16) float cos_s[kRopeTableEntries];
     __shared__ __align__(16) float sin_s[kRopeTableEntries];
