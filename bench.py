@@ -10,7 +10,8 @@ A step is one pass of the three kernels over the rank's rows. `value` is
 aggregate tokens/s with inputs resident in HBM (CUDA events, max over ranks);
 `e2e` is the same metric through the host-buffer API with the host->device and
 device->host copies of every step inside the timed region. `roofline` is for
-the kernel that moves most of the bytes (SwiGLU); `kernels` lists all three.
+the one kernel of the timed region (the chain's three operations share a
+grid); `kernels` lists the three operations launched separately.
 For N > 1 launch under torch.distributed.run (one rank per GPU); a bare
 `--gpus N` re-launches itself that way.
 
