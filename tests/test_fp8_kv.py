@@ -62,6 +62,31 @@ def test_oracle_fp8_properties(orc, fmt):
     assert np.array_equal(back, codes)
 
 
+@pytest.mark.parametrize("fmt", [1, 2])
+def test_oracle_fp8_is_monotone_and_nearest_on_floats(orc, fmt):
+    """Arbitrary floats (the reference-key path feeds differences of halves, not
+    halves): the code is monotone in the magnitude, symmetric in the sign, and
+    decodes to a value within half a grid step of the input inside the finite
+    range (the subnormal range rounds half up, the rest to nearest even)."""
+    R = orc.restated()
+    rng = np.random.default_rng(50 + fmt)
+    top, tiny = (448.0, 2.0 ** -9) if fmt == 1 else (57344.0, 2.0 ** -16)
+    mags = np.sort(np.concatenate([
+        np.exp(rng.uniform(np.log(tiny / 8), np.log(top * 2), 4000)),
+        np.array([tiny / 2, tiny, 2.0 ** (-6 if fmt == 1 else -14), top, top * 1.03], np.float64)])).astype(np.float32)
+    codes = R.fp8_encode(mags, fmt).astype(np.int32)
+    assert (np.diff(codes) >= 0).all()                                    # monotone
+    assert np.array_equal(R.fp8_encode(-mags, fmt).astype(np.int32), codes | 0x80)
+    back = R.fp8_decode(codes.astype(np.uint8), fmt).astype(np.float64)
+    inside = mags <= top
+    M = 3 if fmt == 1 else 2
+    emin = -6 if fmt == 1 else -14
+    expo = np.maximum(np.floor(np.log2(np.maximum(mags[inside].astype(np.float64), 1e-30))), emin)
+    step = np.ldexp(1.0, (expo - M).astype(np.int64))
+    assert (np.abs(back[inside] - mags[inside]) <= 0.5 * step * (1 + 1e-6)).all()
+    assert (codes[~inside] == (0x7E if fmt == 1 else 0x7B)).all()         # saturation above the largest finite value
+
+
 # ------------------------------------------------------------------ GPU
 torch = pytest.importorskip("torch")
 gpu = pytest.mark.gpu
