@@ -30,6 +30,10 @@
  * the layer's reference key subtracted in float when the cache keeps one
  * (kv_quant.cu:68-73), and is encoded; V is encoded as it is. The cache write
  * shrinks from 4096 to 2048 bytes per 7B token.
+ *
+ * Paged caches (template PAGED): logical position t = cache_offset + r lands in
+ * row page_table[t / 64] * 64 + t % 64 of the pool (cache_row below), for every
+ * format; the contiguous instantiations carry no trace of the mapping.
  */
 #include "fp8_kv.cuh"
 #include "rope.cuh"
