@@ -34,6 +34,7 @@ extern std::atomic<uint64_t> g_launches;
 
 constexpr int kLmThreads = 256;
 constexpr int kLmMinRowsPerCta = 32;   /* bounds the number of partials: ceil(V / 32) */
+constexpr int kLmPrefetchBytes = 256 * 1024;   /* per CTA, into L2, during the prologue (296 CTAs: 76 MB) */
 
 struct Best {
     float v;
@@ -75,6 +76,20 @@ lm_head_kernel(const LmHeadArgs a) {
     __shared__ float inv_s;
     __shared__ Best cta_best[8];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    /* this CTA's contiguous block of rows */
+    const int cta_lo = blockIdx.x * a.rows_per_cta;
+    const int cta_hi = min(a.V, cta_lo + a.rows_per_cta);
+
+    /* While x is staged (and normalised: two barriers and a double-precision
+     * reduction, a few microseconds in which the CTA would load nothing), pull
+     * the head of this CTA's block of W into L2. */
+    if (cta_lo < cta_hi) {
+        const char* wbase = reinterpret_cast<const char*>(a.W + (size_t)cta_lo * (size_t)a.nvec);
+        size_t bytes = (size_t)(cta_hi - cta_lo) * (size_t)a.nvec * sizeof(vec16);
+        if (bytes > (size_t)kLmPrefetchBytes) bytes = (size_t)kLmPrefetchBytes;
+        for (size_t off = (size_t)t * 128u; off < bytes; off += (size_t)kLmThreads * 128u)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(wbase + off));
+    }
 
     /* stage x (normalised if asked) as floats */
     if (NORM) {
@@ -112,9 +127,7 @@ lm_head_kernel(const LmHeadArgs a) {
     __syncthreads();
 
     Best best{-FLT_MAX, 0x7fffffff};
-    /* this CTA's contiguous block of rows; its 8 warps take row pairs round-robin */
-    const int cta_lo = blockIdx.x * a.rows_per_cta;
-    const int cta_hi = min(a.V, cta_lo + a.rows_per_cta);
+    /* the CTA's 8 warps take row pairs of its block round-robin */
     for (int r0 = cta_lo + 2 * warp; r0 < cta_hi; r0 += 2 * (kLmThreads / 32)) {
         const int r1 = r0 + 1;
         const bool two = r1 < cta_hi;
