@@ -124,6 +124,7 @@ gather_rows_vec_kernel(const vec16* __restrict__ table, const int32_t* __restric
     /* One CTA per row; 4 independent 16-byte loads per thread per trip. */
     const int row = blockIdx.x;
     int id = ids[row];
+    const int far_id = gather_far_id(ids, row, rows, vocab);
     if (vocab > 0) id = min(max(id, 0), vocab - 1);
     const vec16* sp = table + (size_t)id * (size_t)nvec;
     vec16* dp = out + (size_t)row * (size_t)nvec;
@@ -134,6 +135,7 @@ gather_rows_vec_kernel(const vec16* __restrict__ table, const int32_t* __restric
             const int v = v0 + j * blockDim.x;
             if (v < nvec) r[j] = ld_stream(sp + v);
         }
+        if (v0 == (int)threadIdx.x) gather_prefetch(table, far_id, nvec, threadIdx.x, blockDim.x);
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int v = v0 + j * blockDim.x;
