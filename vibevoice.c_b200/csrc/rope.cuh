@@ -12,6 +12,7 @@ namespace vvb {
 constexpr int kRopeThreads = 256;
 constexpr int kRopeMaxRowsPerThread = 4;
 constexpr int kRopeTableEntries = 1024;   /* rows_per_cta * half <= this */
+constexpr unsigned kRopeOneWave = 3u * 148u;   /* CTAs resident at once on a 148-SM part */
 
 struct RopeArgs {
     vec16* q;
@@ -169,10 +170,20 @@ static inline void rope_plan(RopeArgs& a, void* q, void* k, int rows, int n_q_he
         a.row_slots = kRopeTableEntries / half;
         passes = 1;
     }
+    /* Deep grids take the most rows per thread (36.2 us at 14449 rows with 4
+     * against 40.3 with 2 and 55.6 with 1). A grid that fits the SMs in one wave
+     * is a latency problem instead: it takes the fewest rows per thread that
+     * still fit one wave (1.86 against 2.48 us at 64 rows, 4.43 against 5.08 at
+     * 1024). kRopeOneWave = 3 CTAs on each of 148 SMs. */
+    const unsigned gy_ = (unsigned)((a.items_per_row + kRopeThreads - 1) / kRopeThreads);
+    for (int p = 1; p < passes; p++) {
+        const unsigned ctas = (unsigned)((rows + a.row_slots * p - 1) / (a.row_slots * p)) * gy_;
+        if (ctas <= kRopeOneWave) { passes = p; break; }
+    }
     a.passes = passes;
     const int rows_per_cta = a.row_slots * a.passes;
     *gx = (unsigned)((rows + rows_per_cta - 1) / rows_per_cta);
-    *gy = (unsigned)((a.items_per_row + kRopeThreads - 1) / kRopeThreads);
+    *gy = gy_;
 }
 
 }  // namespace vvb
