@@ -11,7 +11,11 @@ aggregate tokens/s with inputs resident in HBM (CUDA events, max over ranks);
 `e2e` is the same metric through the host-buffer API with the host->device and
 device->host copies of every step inside the timed region. `roofline` is for
 the one kernel of the timed region (the chain's three operations share a
-grid); `kernels` lists the three operations launched separately.
+grid); `chain_ops_separately` times the three entry points alone, and on one
+GPU `kernels` lists every kernel family at the shapes of the benchmark
+configurations (bench_kernels.py), the one-token decode sequence included.
+Every K-step pass is repeated (at least 15 times, and until the timed passes
+add up to a quarter of a second); `ms_per_step` is the median pass.
 For N > 1 launch under torch.distributed.run (one rank per GPU); a bare
 `--gpus N` re-launches itself that way.
 
@@ -44,11 +48,10 @@ BYTES_SWIGLU = 3 * INTER * 2              # read gate, up; write out            
 BYTES_CHAIN = BYTES_ADDNORM + BYTES_ROPE + BYTES_SWIGLU   #                     158 720
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per token per launch seen by ncu (dram__bytes_read.sum +
-# dram__bytes_write.sum at T = 14449, one launch of each kernel; summary in
-# profiles/layer_chain_T14449_launch_list_and_dram.md). Reads equal the
-# algorithmic reads; writes are ~55 MB short of the algorithmic writes because
-# the last lines written are still dirty in L2 when the kernel ends. Scaled by
-# rows for other sizes.
+# dram__bytes_write.sum at T = 14449, one launch of each kernel). Reads equal
+# the algorithmic reads; writes are ~55 MB short of the algorithmic writes
+# because the last lines written are still dirty in L2 when the kernel ends.
+# Scaled by rows for other sizes.
 NCU_DRAM_BYTES_PER_TOKEN = {"layer_chain": 155230, "swiglu": 110050, "add_rmsnorm": 24590, "rope_qk": 12265}
 CPU_SAMPLE_ROWS = 4096
 
@@ -173,21 +176,50 @@ def cpu_chain_run(rows: int, steps: int, warmup: int):
 
 
 def run_reference_arm(args):
+    """`--impl reference`: the reference's CPU kernels on the box's host cores.
+    Rank 0 alone works. The timing runs in a child process whose environment
+    has the OpenMP variables removed: torch.distributed.run exports
+    OMP_NUM_THREADS=1 to its ranks, and vv_cpu_threads() honours that
+    variable (src/cpu/cpu_kernels.c:303-327), which would put the whole CPU
+    baseline on one core."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rows = T_TOTAL
-    value, info = cpu_chain_run(rows, args.steps, args.warmup)
+    info = cpu_chain_subprocess(T_TOTAL, args.steps, args.warmup)
+    value = info.get("value")
     line = {
         "impl": "reference", "metric": "layer_chain_tokens_per_s", "value": value, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": info["ms_per_pass"],
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": info.get("ms_per_pass"),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": info["cores"], "kind": info["kind"],
-                         "sample": info["sample"], "simd": info["simd"], "physical_cores": info["physical_cores"]},
+        "cpu_baseline": info,
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+def cpu_chain_subprocess(rows, steps, warmup):
+    """Times the CPU leg in a child process: the reference pins its OpenMP team
+    (and the calling thread) to cores, which must not leak into this process,
+    and the child must not inherit a launcher's OMP_NUM_THREADS."""
+    env = {k: v for k, v in os.environ.items()
+           if not (k.startswith("OMP_") or k.startswith("GOMP_") or k.startswith("KMP_") or k == "MKL_NUM_THREADS")}
+    env["CUDA_VISIBLE_DEVICES"] = ""
+    try:
+        out = subprocess.run([sys.executable, os.path.abspath(__file__), "--cpu-worker", f"{rows},{steps},{warmup}"],
+                             capture_output=True, text=True, timeout=900, check=True, env=env).stdout
+        return json.loads(out.strip().splitlines()[-1])
+    except Exception as e:  # the GPU line is still valid without it
+        return {"value": None, "unit": "tokens/s", "error": f"{type(e).__name__}: {e}"[:300]}
+
+
+def cpu_worker(spec):
+    rows, steps, warmup = (int(x) for x in spec.split(","))
+    value, info = cpu_chain_run(rows, steps, warmup)
+    print(json.dumps({"value": value, "unit": "tokens/s", "cores": info["cores"], "kind": info["kind"],
+                      "sample": info["sample"], "simd": info["simd"], "physical_cores": info["physical_cores"],
+                      "ms_per_pass": info["ms_per_pass"],
+                      "omp_num_threads_env": os.environ.get("OMP_NUM_THREADS")}))
 
 
 def workload_config(n_gpus, scaling="strong", rows=T_TOTAL):
@@ -202,6 +234,10 @@ def workload_config(n_gpus, scaling="strong", rows=T_TOTAL):
 
 
 # --------------------------------------------------------------------------- GPU arm
+MIN_REPEATS = 15            # K-step passes timed in one process
+MIN_REGION_S = 0.25         # and as many more as it takes for the timed passes to add up to this
+
+
 def run_native(args):
     import torch
     import torch.distributed as dist
@@ -221,19 +257,13 @@ def run_native(args):
         if world > 1:
             dist.barrier()
 
-    def reduce_max(x: float) -> float:
+    def reduce(values, op):
+        """Element-wise max / sum over ranks of a list of floats (one collective)."""
         if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    def reduce_sum(x: float) -> float:
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
+            return list(values)
+        t = torch.tensor(list(values), dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.SUM)
+        return t.tolist()
 
     total_rows = args.rows * (world if args.scaling == "weak" else 1)
     first, rows = vv.vvb_shard_rows(total_rows, world, rank)
@@ -252,7 +282,7 @@ def run_native(args):
     stream = torch.cuda.current_stream()
 
     def restore():
-        # the chain works in place; start every pass set from the same values
+        # the chain works in place; start every pass from the same values
         h.copy_(h0)
         gate.copy_(g0)
 
@@ -292,65 +322,146 @@ def run_native(args):
         sampler = ClockSampler(uuid, local)
         sampler.start()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    torch.cuda.synchronize()
-
-    # ---- pass A: K steps back to back, one event pair; this is `value`
-    restore()
-    torch.cuda.synchronize()
-    barrier()
+    K = args.steps
+    warm = max(args.warmup, 3)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches0 = vv.launch_count()
-    t_region0 = time.perf_counter()
     e0.record(stream)
-    for _ in range(args.steps):
+    for _ in range(warm):
         step()
     e1.record(stream)
     torch.cuda.synchronize()
-    t_region1 = time.perf_counter()
-    launches = vv.launch_count() - launches0 if graph is None else nodes_per_step * args.steps
-    barrier()
-    ms_total = reduce_max(e0.elapsed_time(e1))
-    launches_all = int(reduce_sum(float(launches)))
+    est_ms = max(reduce([e0.elapsed_time(e1) / warm], "max")[0], 1e-3)
+    repeats = args.repeats or min(2000, max(MIN_REPEATS, int(MIN_REGION_S * 1e3 / (K * est_ms)) + 1))
 
-    # ---- pass B: the same K steps with an event between launches: per-kernel durations
+    # ---- timed passes: EXACTLY K steps under one CUDA-event pair, a barrier and a
+    # synchronize on both sides, `repeats` times; ms_per_step is the median pass
+    # (each pass: max over ranks) / K
+    launches0 = vv.launch_count()
+    pass_ms = []
+    t_region0 = time.perf_counter()
+    for _ in range(repeats):
+        restore()
+        torch.cuda.synchronize()
+        barrier()
+        e0.record(stream)
+        for _ in range(K):
+            step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        barrier()
+        pass_ms.append(e0.elapsed_time(e1))
+    t_region1 = time.perf_counter()
+    launches = (vv.launch_count() - launches0) if graph is None else nodes_per_step * K * repeats
+    pass_ms = reduce(pass_ms, "max")
+    launches_all = int(reduce([float(launches)], "sum")[0])
+
+    # ---- span pass: repeats x K steps back to back, host clock from the barrier's
+    # return to every rank synchronised: start skew between GPUs is inside it
     restore()
     torch.cuda.synchronize()
     barrier()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
-    for s in range(args.steps):
-        ev[s][0].record(stream)
-        vv.check(vv.vvb_add_rmsnorm_dev(h, d, w, normed, rows, H, EPS, stream))
-        ev[s][1].record(stream)
-        vv.check(vv.vvb_rope_qk_dev(q, k, rows, NQ, NKV, HD, first, None, THETA, stream))
-        ev[s][2].record(stream)
-        vv.check(vv.vvb_swiglu_dev(gate, up, gate, rows * INTER, stream))
-        ev[s][3].record(stream)
+    t0 = time.perf_counter()
+    for _ in range(repeats * K):
+        step()
     torch.cuda.synchronize()
     barrier()
-    per = {}
-    for i, name in enumerate(("add_rmsnorm", "rope_qk", "swiglu")):
-        per[name] = reduce_max(statistics.fmean(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)))
-    ms_total_b = reduce_max(ev[0][0].elapsed_time(ev[-1][3]))
-
+    span_s = reduce([time.perf_counter() - t0], "max")[0]
     clocks = sampler.stop(t_region0, t_region1) if sampler else None
 
+    # ---- the chain's three operations launched separately at this rank's rows (same protocol)
+    restore()
+    per = separate_ops(torch, vv, (h, d, w, normed, q, k, gate, up), rows, first, stream, reduce, barrier)
+
     # ---- e2e: host buffers through the pipeline API, copies inside the timed region
-    if args.no_e2e:
-        e2e_line = None
-    else:
+    e2e_line = None
+    if not args.no_e2e:
         e2e_line = run_e2e(args, vv, torch, (h0, d, w, q, k, g0, up), rows, first, local, total_rows,
-                           barrier, reduce_max, reduce_sum)
+                           barrier, reduce)
+
+    kernels = None
+    if world == 1 and not args.no_kernels:
+        del h, d, q, k, gate, up, normed, h0, g0
+        torch.cuda.empty_cache()
+        import bench_kernels
+        kernels = bench_kernels.run(*measured_hbm_peak())
 
     if world > 1:
         dist.destroy_process_group()
     if rank != 0:
         return
-    emit(args, world, total_rows, ms_total, ms_total_b, per, launches_all, clocks, e2e_line)
+    emit(args, world, total_rows, pass_ms, span_s, repeats, per, launches_all, clocks, e2e_line, kernels)
 
 
-def run_e2e(args, vv, torch, tensors, rows, first, local, total_rows, barrier, reduce_max, reduce_sum):
+def separate_ops(torch, vv, tensors, rows, first, stream, reduce, barrier):
+    """add+RMSNorm, RoPE and SwiGLU as three entry points, each ALONE: 20 launches
+    back to back under one event pair (no event between launches), five times,
+    median; the rank's tensors exceed the L2 at every N."""
+    h, d, w, normed, q, k, gate, up = tensors
+    ops = {
+        "add_rmsnorm": lambda: vv.check(vv.vvb_add_rmsnorm_dev(h, d, w, normed, rows, H, EPS, stream)),
+        "rope_qk": lambda: vv.check(vv.vvb_rope_qk_dev(q, k, rows, NQ, NKV, HD, first, None, THETA, stream)),
+        "swiglu": lambda: vv.check(vv.vvb_swiglu_dev(gate, up, gate, rows * INTER, stream)),
+    }
+    out = {}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, fn in ops.items():
+        for _ in range(3):
+            fn()
+        res = []
+        for _ in range(5):
+            torch.cuda.synchronize()
+            barrier()
+            e0.record(stream)
+            for _ in range(20):
+                fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            res.append(e0.elapsed_time(e1) / 20)
+        out[name] = statistics.median(reduce(res, "max"))
+    return out
+
+
+def copy_ceiling(torch, local, h2d_bytes, d2h_bytes, barrier, reduce, rounds=3):
+    """What the box's host<->device path gives this rank while every rank does
+    the same: plain cudaMemcpyAsync of the step's byte counts from and to pinned
+    memory, uploads on one stream and downloads on another, no kernels. The
+    copies go in 64 MiB pieces (one call per piece)."""
+    piece = 64 << 20
+    hb = torch.empty(piece, dtype=torch.uint8).pin_memory()
+    hb2 = torch.empty(piece, dtype=torch.uint8).pin_memory()
+    db = torch.empty(piece, dtype=torch.uint8, device="cuda")
+    db2 = torch.empty(piece, dtype=torch.uint8, device="cuda")
+    s_up, s_down = torch.cuda.Stream(), torch.cuda.Stream()
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+
+    def one_round():
+        torch.cuda.synchronize()
+        barrier()
+        e0.record(s_up)
+        s_down.wait_event(e0)
+        left = h2d_bytes
+        with torch.cuda.stream(s_up):
+            while left > 0:
+                n = min(piece, left)
+                db[:n].copy_(hb[:n], non_blocking=True)
+                left -= n
+            e1.record(s_up)
+        left = d2h_bytes
+        with torch.cuda.stream(s_down):
+            while left > 0:
+                n = min(piece, left)
+                hb2[:n].copy_(db2[:n], non_blocking=True)
+                left -= n
+            e2.record(s_down)
+        torch.cuda.synchronize()
+        return max(e0.elapsed_time(e1), e0.elapsed_time(e2))
+
+    one_round()
+    ms = statistics.median(reduce([one_round() for _ in range(rounds)], "max"))
+    return ms
+
+
+def run_e2e(args, vv, torch, tensors, rows, first, local, total_rows, barrier, reduce):
     h0, d, w, q, k, g0, up = tensors
     pin = lambda t: t.cpu().pin_memory()
     hh, hd_, hw, hq, hk, hg, hu = (pin(t) for t in (h0, d, w, q, k, g0, up))
@@ -360,81 +471,86 @@ def run_e2e(args, vv, torch, tensors, rows, first, local, total_rows, barrier, r
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
     for _ in range(2):
         vv.check(pipe.run(hchain), "vvb_layer_chain_host")
-    barrier()
-    dev_ms, t0 = 0.0, time.perf_counter()
+    dev_ms, wall_ms = [], []
     for _ in range(e2e_steps):
+        barrier()
+        t0 = time.perf_counter()
         vv.check(pipe.run(hchain), "vvb_layer_chain_host")
-        dev_ms += pipe.last_ms()
-    wall_ms = 1e3 * (time.perf_counter() - t0)
+        wall_ms.append(1e3 * (time.perf_counter() - t0))
+        dev_ms.append(pipe.last_ms())
     h2d, d2h = pipe.last_traffic()
     barrier()
-    e2e_ms = reduce_max(dev_ms)
-    e2e_wall_ms = reduce_max(wall_ms)
-    h2d_all, d2h_all = int(reduce_sum(float(h2d))), int(reduce_sum(float(d2h)))
+    dev_ms = reduce(dev_ms, "max")           # per step: the slowest rank
+    wall_ms = reduce(wall_ms, "max")
+    h2d_all, d2h_all = (int(x) for x in reduce([float(h2d), float(d2h)], "sum"))
     pipe.close()
-    return {"value": total_rows * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
+    del pipe
+    ms = statistics.median(dev_ms)
+    ceiling_ms = copy_ceiling(torch, local, h2d, d2h, barrier, reduce)
+    return {"value": total_rows / (ms * 1e-3), "unit": "tokens/s",
             "h2d_bytes_per_step": h2d_all, "d2h_bytes_per_step": d2h_all, "steps": e2e_steps,
-            "ms_per_step": e2e_ms / e2e_steps, "wall_ms_per_step": e2e_wall_ms / e2e_steps,
+            "ms_per_step": ms, "ms_min": min(dev_ms), "ms_max": max(dev_ms),
+            "wall_ms_per_step": statistics.median(wall_ms),
+            "ceiling": {"value": total_rows / (ceiling_ms * 1e-3), "unit": "tokens/s", "ms_per_step": ceiling_ms,
+                        "what": "every rank copying its step's bytes host->device and device->host at once with "
+                                "plain cudaMemcpyAsync from/to pinned memory, no kernels"},
+            "frac_of_ceiling": ceiling_ms / ms,
             "api": "vvb_layer_chain_host (pinned host tensors; uploads, kernels and downloads pipelined in "
                    f"{args.slice_rows}-row slices)"}
 
 
-def emit(args, world, total_rows, ms_total, ms_total_b, per, launches_all, clocks, e2e_line):
+def emit(args, world, total_rows, pass_ms, span_s, repeats, per, launches_all, clocks, e2e_line, kernels):
     peak, peak_kind = measured_hbm_peak()
+    K = args.steps
     rows_max = -(-total_rows // world)       # the slowest rank holds ceil(T/N) rows
-    kernels = {}
+    ms_step = statistics.median(pass_ms) / K
+    ops = {}
     for name, bpt in (("add_rmsnorm", BYTES_ADDNORM), ("rope_qk", BYTES_ROPE), ("swiglu", BYTES_SWIGLU)):
         gbs = bpt * rows_max / (per[name] * 1e-3) / 1e9
-        kernels[name] = {"ms": per[name], "GB/s": gbs, "frac_of_" + peak_kind: gbs / peak,
-                         "algorithmic_bytes_per_launch": bpt * rows_max}
+        ops[name] = {"us": per[name] * 1e3, "GB/s": gbs, "frac_of_" + peak_kind: gbs / peak,
+                     "frac_of_nominal_8TBs": gbs / 8000.0, "algorithmic_bytes_per_launch": bpt * rows_max}
     # The timed region launches ONE kernel per step (layer_chain_kernel: the three operations share a
-    # grid), so that kernel is the dominant one; `kernels` breaks it down with the separate entry points.
-    chain_gbs = BYTES_CHAIN * rows_max / (ms_total / args.steps * 1e-3) / 1e9
+    # grid), so that kernel is the dominant one; `chain_ops_separately` times the three entry points alone.
+    chain_gbs = BYTES_CHAIN * rows_max / (ms_step * 1e-3) / 1e9
     traffic = NCU_DRAM_BYTES_PER_TOKEN["layer_chain"]
+    value = total_rows / (ms_step * 1e-3)
+    value_span = total_rows * repeats * K / span_s
     line = {
-        "metric": "layer_chain_tokens_per_s", "value": total_rows * args.steps / (ms_total * 1e-3),
-        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": args.scaling,
+        "metric": "layer_chain_tokens_per_s", "value": value,
+        "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
         "vs_baseline": None, "dtype": "f16 storage, f32 arithmetic (f64 sum of squares)", "data": "synthetic",
         "config": workload_config(world, args.scaling, args.rows),
+        "timing": {"repeats": repeats, "what": "each repeat = exactly K steps under one CUDA-event pair, barrier + "
+                   "synchronize on both sides, max over ranks; ms_per_step = median repeat / K",
+                   "ms_per_step_min": min(pass_ms) / K, "ms_per_step_max": max(pass_ms) / K,
+                   "spread": (max(pass_ms) - min(pass_ms)) / statistics.median(pass_ms),
+                   "timed_region_s": sum(pass_ms) * 1e-3,
+                   "value_span": value_span, "span_s": span_s,
+                   "span_what": "host clock from a barrier's return to every rank synchronised, over "
+                                f"{repeats * K} steps issued back to back (start skew between GPUs is inside it)",
+                   "span_over_events": value_span / value},
         "roofline": {"bound": "hbm", "kernel": "layer_chain_kernel (add+RMSNorm | RoPE Q,K | SwiGLU in one grid)",
                      "achieved": chain_gbs, "peak": peak, "unit": "GB/s", "frac": chain_gbs / peak,
-                     "peak_kind": "of " + peak_kind,
+                     "peak_kind": "of " + peak_kind, "frac_of_nominal_8TBs": chain_gbs / 8000.0,
                      "algorithmic_bytes_per_launch": BYTES_CHAIN * rows_max,
                      "traffic": None if traffic is None else traffic * rows_max,
-                     "timing": "one CUDA-event pair around the K timed launches on the launching stream "
+                     "timing": "CUDA events around K launches on the launching stream "
                                "(ms_per_step is the kernel's average duration, launch gaps included)"},
-        "kernels_note": "the chain's operations launched separately in a second pass of K steps with a CUDA event "
-                        "between launches (durations include the event gaps; ms_per_step_with_events = "
-                        f"{ms_total_b / args.steps:.4f})",
-        "kernels": kernels,
+        "chain_ops_separately": ops,
         "e2e": e2e_line,
         "gpu_launches": launches_all,
         "launch_mode": ("direct" if args.no_graph else "one CUDA graph replay per step") +
-                       f" ({launches_all // max(1, args.steps * world)} kernel launch(es) per step per GPU: the chain's "
-                       "three operations share one grid)",
+                       f" ({launches_all // max(1, K * repeats * world)} kernel launch(es) per step per GPU: the chain's "
+                       "three operations share one grid); gpu_launches counts all timed repeats",
         "clocks": clocks,
     }
-    if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline_subprocess()
+    if kernels is not None:
+        line["kernels"] = kernels["cases"]
+        line["kernels_method"] = kernels["method"]
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_chain_subprocess(CPU_SAMPLE_ROWS, 20, 2)
     print(json.dumps(line), flush=True)
-
-
-def cpu_baseline_subprocess():
-    """Times the CPU leg in a child process: the reference pins its OpenMP team
-    (and the calling thread) to cores, which must not leak into this process."""
-    try:
-        out = subprocess.run([sys.executable, os.path.abspath(__file__), "--cpu-baseline-worker"],
-                             capture_output=True, text=True, timeout=600, check=True).stdout
-        return json.loads(out.strip().splitlines()[-1])
-    except Exception as e:  # the GPU line is still valid without it
-        return {"value": None, "unit": "tokens/s", "error": f"{type(e).__name__}: {e}"[:200]}
-
-
-def cpu_baseline_worker():
-    value, info = cpu_chain_run(CPU_SAMPLE_ROWS, steps=20, warmup=2)
-    print(json.dumps({"value": value, "unit": "tokens/s", "cores": info["cores"], "kind": info["kind"],
-                      "sample": info["sample"], "simd": info["simd"], "physical_cores": info["physical_cores"]}))
 
 
 def main():
@@ -458,11 +574,14 @@ def main():
     ap.add_argument("--case", default=None, help="--workload kernels: run only the cases whose name contains this")
     ap.add_argument("--plain-launches", action="store_true",
                     help="--workload kernels: four direct launches per case, no graphs, no timing (profiler captures)")
-    ap.add_argument("--cpu-baseline-worker", action="store_true", help=argparse.SUPPRESS)
+    ap.add_argument("--repeats", type=int, default=0,
+                    help="timed K-step passes (default: at least 15, and enough for a 0.25 s timed region)")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel list of the 1-GPU line")
+    ap.add_argument("--cpu-worker", default=None, help=argparse.SUPPRESS)
     args = ap.parse_args()
 
-    if args.cpu_baseline_worker:
-        return cpu_baseline_worker()
+    if args.cpu_worker:
+        return cpu_worker(args.cpu_worker)
     if args.gpus > 1 and "RANK" not in os.environ:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 1000),
@@ -474,8 +593,8 @@ def main():
         import torch
         assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
         torch.cuda.set_device(0)
-        from vvb200 import kernel_bench
-        return kernel_bench.main(*measured_hbm_peak(), only=args.case, plain=args.plain_launches)
+        import bench_kernels
+        return bench_kernels.main(*measured_hbm_peak(), only=args.case, plain=args.plain_launches)
     return run_native(args)
 
 

@@ -1,0 +1,344 @@
+"""Per-kernel timings of libvvb200 at the shapes of the benchmark configurations:
+`python bench.py --workload kernels`, and the `kernels` list of the default
+bench line.
+
+Protocol, the same for every case: the op alone on a stream, `iters` launches
+back to back captured in one CUDA graph (no event between launches, so the
+programmatic dependent launch of consecutive kernels stays in effect), over
+buffer sets that rotate through more than 2.5x the L2 so that every launch
+reads cold HBM even when one set would fit in the cache; the graph is replayed
+five times under one CUDA-event pair each and the MEDIAN replay divided by
+`iters` is the figure (`min_us` beside it). A second figure, `warm_us`, replays
+over a single buffer set (L2-resident for the small shapes) and is the launch
+latency a decode step sees; it is never reported as HBM bandwidth. The SM
+clock is read through NVML after each case.
+
+`decode step` is one M = 1 token of the 28-layer model, row kernels only (the
+GEMMs and the attention between them belong to the engine): this library's
+four launches per layer, and beside it the same sequence made of the
+reference's own CUDA kernels when that library was built (oracle/_ref).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+import statistics
+
+import torch
+
+import vvb200 as vv
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+REF_CUDA = os.path.join(ROOT, "oracle", "_ref", "libvvref_cuda.so")
+H, NQ, NKV, HD, INTER, VOCAB, T = 3584, 28, 4, 128, 18944, 151936, 14449
+L2_BYTES = 126e6
+NOMINAL_HBM_GBS = 8000.0
+REPLAYS = 5
+
+
+class _Clock:
+    def __init__(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+        except Exception:
+            self.nv = None
+
+    def sm_mhz(self):
+        if self.nv is None:
+            return None
+        try:
+            return int(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+        except Exception:
+            return None
+
+
+def time_graph(fn, nsets, iters, clock=None):
+    """(median us, min us, SM MHz right after the last replay) per launch of fn(set_index, stream)."""
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for i in range(min(nsets, 3)):
+            fn(i % nsets, s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for i in range(iters):
+                fn(i % nsets, s)
+        g.replay()
+        torch.cuda.synchronize()
+        res = []
+        mhz = None
+        for _ in range(REPLAYS):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(s)
+            g.replay()
+            e1.record(s)
+            if clock is not None:
+                mhz = clock.sm_mhz()          # read while the replay is in flight
+            torch.cuda.synchronize()
+            res.append(e0.elapsed_time(e1) * 1e3 / iters)
+    return statistics.median(res), min(res), mhz
+
+
+def _nsets(bytes_per_set):
+    return max(1, min(48, int(2.5 * L2_BYTES / bytes_per_set) + 1))
+
+
+class Runner:
+    def __init__(self, peak_gbs, peak_kind, only=None, plain=False):
+        self.peak, self.kind, self.only, self.plain = peak_gbs, peak_kind, only, plain
+        self.clock = _Clock()
+        self.out = []
+
+    def wanted(self, name):
+        return self.only is None or self.only in name
+
+    def case(self, name, config, make_set, call, set_bytes, algo_bytes, iters=40):
+        if not self.wanted(name):
+            return
+        if self.plain:
+            # a handful of direct launches over two buffer sets: what a profiler capture wants
+            sets = [make_set() for _ in range(2)]
+            s = torch.cuda.current_stream()
+            for i in range(4):
+                call(sets[i % 2], s)
+            torch.cuda.synchronize()
+            self.out.append({"case": name, "plain_launches": 4})
+            return
+        ns = _nsets(set_bytes)
+        sets = [make_set() for _ in range(ns)]
+        cold, cold_min, mhz = time_graph(lambda i, s: call(sets[i], s), ns, iters, self.clock)
+        warm, _, _ = time_graph(lambda i, s: call(sets[0], s), 1, iters)
+        gbs = algo_bytes / cold / 1e3
+        del sets
+        torch.cuda.empty_cache()
+        self.out.append({"case": name, "config": config, "us": round(cold, 2), "min_us": round(cold_min, 2),
+                         "GB/s": round(gbs, 1), "frac_of_" + self.kind: round(gbs / self.peak, 3),
+                         "frac_of_nominal_8TBs": round(gbs / NOMINAL_HBM_GBS, 3),
+                         "algorithmic_bytes": algo_bytes, "buffer_sets": ns, "warm_us": round(warm, 2),
+                         "sm_mhz": mhz})
+
+
+def _ok(st):
+    assert st == 0, st
+
+
+def run(peak_gbs: float, peak_kind: str, only=None, plain=False):
+    dev = torch.device("cuda", torch.cuda.current_device())
+    rn = lambda *s: torch.randn(*s, device=dev).half()
+    f16 = lambda *s: torch.empty(*s, device=dev, dtype=torch.float16)
+    w = (1 + 0.02 * torch.randn(H, device=dev)).half()
+    R = Runner(peak_gbs, peak_kind, only, plain)
+
+    # config 1 (and the same op at prefill sizes): residual add + RMSNorm
+    for rows, cfg in ((512, 1), (4096, None), (T, 5)):
+        R.case(f"add_rmsnorm [{rows},3584]", cfg, lambda: (rn(rows, H), rn(rows, H), f16(rows, H)),
+               lambda b, s: _ok(vv.vvb_add_rmsnorm_dev(b[0], b[1], w, b[2], rows, H, 1e-6, s)),
+               rows * H * 2 * 3, rows * H * 2 * 4 + 2 * H)
+    # config 2: RoPE prefill, Q [rows,28,128] + K [rows,4,128]
+    for rows, cfg in ((4096, 2), (T, 5)):
+        R.case(f"rope_qk [{rows},28+4,128]", cfg, lambda: (rn(rows, NQ, HD), rn(rows, NKV, HD)),
+               lambda b, s: _ok(vv.vvb_rope_qk_dev(b[0], b[1], rows, NQ, NKV, HD, 0, None, 1e6, s)),
+               rows * (NQ + NKV) * HD * 2, 2 * rows * (NQ + NKV) * HD * 2)
+    # config 3: SwiGLU in place on gate; the decode shape [64, 18944]
+    for rows, cfg in ((4096, 3), (64, 3), (T, 5)):
+        R.case(f"swiglu [{rows},18944]", cfg, lambda: (rn(rows, INTER), rn(rows, INTER)),
+               lambda b, s: _ok(vv.vvb_swiglu_dev(b[0], b[1], b[0], rows * INTER, s)),
+               rows * INTER * 2 * 2, rows * INTER * 2 * 3, iters=20 if rows > 4096 else 40)
+    # config 4: gather 16384 rows of [151936, 3584] + RMSNorm (fused), and the plain gather
+    rows = 16384
+    if R.wanted("embedding"):
+        table = torch.empty(VOCAB, H, device=dev, dtype=torch.float16).normal_(0, 0.02)
+        mk_ids = lambda: torch.randint(0, VOCAB, (rows,), device=dev, dtype=torch.int32)
+        R.case("embedding_rmsnorm 16384 of [151936,3584]", 4, lambda: (mk_ids(), f16(rows, H), f16(rows, H)),
+               lambda b, s: _ok(vv.vvb_embedding_rmsnorm_dev(table, b[0], b[1], w, b[2], rows, H, VOCAB, 1e-6, s)),
+               rows * H * 2 * 3, rows * H * 2 * 3 + rows * 4 + 2 * H, iters=20)
+        R.case("embedding 16384 of [151936,3584]", 4, lambda: (mk_ids(), f16(rows, H)),
+               lambda b, s: _ok(vv.vv_embedding_dev(table, b[0], b[1], rows, H, s)),
+               rows * H * 2 * 2, rows * H * 2 * 2 + rows * 4, iters=20)
+        del table
+        torch.cuda.empty_cache()
+    # flat element-wise ops of the same translation unit in the reference
+    rows = T
+    R.case("residual_add [14449,3584]", None, lambda: (rn(rows, H), rn(rows, H)),
+           lambda b, s: _ok(vv.vvb_residual_add_dev(b[0], b[1], rows * H, s)),
+           rows * H * 4, rows * H * 6)
+    bias = rn(NQ * HD)
+    R.case("bias_add [14449,3584]", None, lambda: (rn(rows, NQ * HD),),
+           lambda b, s: _ok(vv.vv_bias_add_dev(b[0], bias, rows, NQ * HD, s)),
+           rows * H * 2, rows * H * 4 + 2 * H)
+    # bias + RoPE + KV-cache append in one launch (Q in place; K, V read once and written into the cache)
+    bq, bk, bv = rn(NQ * HD), rn(NKV * HD), rn(NKV * HD)
+    R.case("rope_qk_append [14449,28+4+4,128] with biases", None,
+           lambda: (rn(rows, NQ, HD), rn(rows, NKV, HD), rn(rows, NKV, HD), f16(rows, NKV * HD), f16(rows, NKV * HD)),
+           lambda b, s: _ok(vv.vvb_rope_qk_append_dev(b[0], b[1], b[2], bq, bk, bv, b[3], b[4], rows, NQ, NKV, HD, 0, 0,
+                                                      None, 1e6, 0, s)),
+           rows * (NQ + 4 * NKV) * HD * 2, rows * (2 * NQ + 4 * NKV) * HD * 2)
+    # the same launch for the FP8 (E4M3) KV cache: K and V leave as one byte per element, K minus a reference key
+    kref = rn(NKV * HD)
+    u8 = lambda *s: torch.empty(*s, device=dev, dtype=torch.uint8)
+    R.case("rope_qk_append_fp8 [14449,28+4+4,128] with biases, e4m3 cache, reference key", None,
+           lambda: (rn(rows, NQ, HD), rn(rows, NKV, HD), rn(rows, NKV, HD), u8(rows, NKV * HD), u8(rows, NKV * HD)),
+           lambda b, s: _ok(vv.vvb_rope_qk_append_fp8_dev(b[0], b[1], b[2], bq, bk, bv, b[3], b[4], kref, rows, NQ, NKV,
+                                                          HD, 0, 0, None, 1e6, vv.VVB_KV_FP8_E4M3, 0, s)),
+           rows * (NQ + 2 * NKV) * HD * 2 + rows * 2 * NKV * HD,
+           rows * (2 * NQ + 2 * NKV) * HD * 2 + rows * 2 * NKV * HD)
+
+    # int8 activation quantizers at long-prompt prefill size (14449 rows), with run sums
+    def qbufs(K):
+        return (torch.empty(rows, K, device=dev, dtype=torch.int8), torch.empty(rows, device=dev, dtype=torch.float32),
+                torch.empty(rows, K // 32, device=dev, dtype=torch.int32))
+
+    qout = lambda K: rows * (K + 4 + K // 8)
+    for layout, lname in ((0, "natural"), (3, "w4_mma")):
+        R.case(f"rmsnorm_q8 [14449,3584] {lname}", None, lambda: (rn(rows, H),) + qbufs(H),
+               lambda b, s: _ok(vv.vv_rmsnorm_q8_dev(b[0], w, rows, H, 1e-6, layout, b[1], b[2], b[3], s)),
+               rows * H * 2 + qout(H), rows * H * 2 + 2 * H + qout(H))
+        R.case(f"swiglu_q8 [14449,18944] {lname}", None, lambda: (rn(rows, INTER), rn(rows, INTER)) + qbufs(INTER),
+               lambda b, s: _ok(vv.vv_swiglu_q8_dev(b[0], b[1], rows, INTER, layout, b[2], b[3], b[4], s)),
+               rows * INTER * 4 + qout(INTER), rows * INTER * 4 + qout(INTER), iters=20)
+    R.case("act_quant [14449,3584] natural", None, lambda: (rn(rows, H),) + qbufs(H),
+           lambda b, s: _ok(vv.vv_act_quant_dev(b[0], rows, H, 0, b[1], b[2], b[3], s)),
+           rows * H * 2 + qout(H), rows * H * 2 + qout(H))
+
+    # the decode tail: final RMSNorm + LM head [152064, 3584] + argmax (two launches), and the plain GEMV
+    V = 152064
+    need_head = R.wanted("lm_head") or R.wanted("decode step")
+    if need_head:
+        head = torch.empty(V, H, device=dev, dtype=torch.float16).normal_(0, 0.02)
+        sbytes = vv.vvb_lm_head_scratch_bytes(V)
+        mk = lambda: (rn(H), u8(sbytes), torch.empty(1, device=dev, dtype=torch.int32),
+                      torch.empty(V, device=dev, dtype=torch.float32))
+        R.case("final_norm + lm_head + argmax [152064,3584]", None, mk,
+               lambda b, s: _ok(vv.vvb_lm_head_argmax_dev(b[0], w, 1e-6, head, V, H, None, b[1], sbytes, b[2], None, s)),
+               V * H * 2, V * H * 2 + 2 * H * 2, iters=10)
+        R.case("lm_head_gemv [152064,3584] (logits)", None, mk,
+               lambda b, s: _ok(vv.vv_lm_head_gemv_dev(b[0], head, b[3], V, H, s)),
+               V * H * 2, V * H * 2 + V * 4, iters=10)
+        if not plain and R.wanted("decode step"):
+            R.out.append(decode_step(dev, head, w, R.clock))
+        del head
+        torch.cuda.empty_cache()
+    return {"workload": "kernels", "peak_GB/s": peak_gbs, "peak_kind": "of " + peak_kind,
+            "nominal_GB/s": NOMINAL_HBM_GBS,
+            "method": "each op alone: CUDA-graph replay of back-to-back launches over rotating buffer sets > 2.5x L2, "
+                      "one CUDA-event pair per replay, median of 5 replays; warm_us = one L2-resident set",
+            "cases": R.out}
+
+
+def load_reference_cuda():
+    """ctypes face of the reference's own CUDA kernels (oracle/_ref/libvvref_cuda.so,
+    built from the reference tree where it is mounted); None where absent."""
+    if not os.path.exists(REF_CUDA):
+        return None
+    ref = C.CDLL(REF_CUDA)
+    vp, i, f = C.c_void_p, C.c_int, C.c_float
+    ref.vv_rmsnorm_dev.argtypes = [vp, vp, vp, i, i, f, vp]
+    ref.vv_residual_add_dev.argtypes = [vp, vp, i, vp]
+    ref.vv_rope_dev.argtypes = [vp, i, i, i, i, vp, f, vp]
+    ref.vv_swiglu_dev.argtypes = [vp, vp, vp, i, vp]
+    ref.vv_embedding_dev.argtypes = [vp, vp, vp, i, i, vp]
+    ref.vv_bias_add_dev.argtypes = [vp, vp, i, i, vp]
+    ref.vv_lm_head_gemv_dev.argtypes = [vp, vp, vp, i, i, vp]
+    ref.vv_argmax_dev.argtypes = [vp, i, vp, vp, vp, vp, vp]
+    if hasattr(ref, "vv_kv_store_dev"):
+        ref.vv_kv_store_dev.argtypes = [vp, vp, vp, vp, vp, vp, vp, C.c_bool, i, i, i, vp, i, i, vp, vp]
+    return ref
+
+
+def decode_step(dev, head, w, clock):
+    """One decode token (M = 1) of the 28-layer model, this library's kernels only:
+    embedding + first norm, then per layer [residual add + norm (layers 1..)] ->
+    bias + RoPE + KV append at the device position -> residual add + norm -> SwiGLU,
+    then the last residual add and final norm + LM head + argmax; one CUDA graph,
+    replayed. Launch-bound: microseconds per token. Beside it the sequence the
+    reference's engine issues for the same work with its own kernels
+    (src/inference/decoder.c:810-988, pipeline.c:1962-1986): rmsnorm, bias x3,
+    rope x2, one cache store, residual add, rmsnorm, swiglu, residual add per
+    layer (its raw cache appends with two positioned copies; the single
+    vv_kv_store_dev launch used here is the cheaper of its two forms)."""
+    rn = lambda *s: torch.randn(*s, device=dev).half()
+    L, max_len, V = 28, 64, head.shape[0]
+    sbytes = vv.vvb_lm_head_scratch_bytes(V)
+    # The token the head picks is embedded by the next replay, so the table must have a row for
+    # every token the head can pick: the head's own rows serve (tied embeddings). The reference's
+    # gather does not check ids (src/cuda/embedding.cu:34-35); a shorter table would be read out
+    # of bounds by it.
+    table = head
+    tok = torch.zeros(1, device=dev, dtype=torch.int32)
+    hid, dlt, nrm = rn(1, H), rn(1, H), rn(1, H)
+    q1, k1, v1, g1, u1 = rn(1, NQ, HD), rn(1, NKV, HD), rn(1, NKV, HD), rn(1, INTER), rn(1, INTER)
+    bq, bk, bv = rn(NQ * HD), rn(NKV * HD), rn(NKV * HD)
+    kc = [torch.zeros(max_len, NKV * HD, device=dev, dtype=torch.float16) for _ in range(L)]
+    vc = [torch.zeros(max_len, NKV * HD, device=dev, dtype=torch.float16) for _ in range(L)]
+    dpos = torch.tensor([7], device=dev, dtype=torch.int32)
+    scr = torch.empty(sbytes, device=dev, dtype=torch.uint8)
+
+    def ours(_i, s):
+        _ok(vv.vvb_embedding_rmsnorm_dev(table, tok, hid, w, nrm, 1, H, V, 1e-6, s))
+        for layer in range(L):
+            if layer:
+                _ok(vv.vvb_add_rmsnorm_dev(hid, dlt, w, nrm, 1, H, 1e-6, s))
+            _ok(vv.vvb_rope_qk_append_dev(q1, k1, v1, bq, bk, bv, kc[layer], vc[layer], 1, NQ, NKV, HD, 0, 0, dpos,
+                                          1e6, 0, s))
+            _ok(vv.vvb_add_rmsnorm_dev(hid, dlt, w, nrm, 1, H, 1e-6, s))
+            _ok(vv.vvb_swiglu_dev(g1, u1, g1, INTER, s))
+        _ok(vv.vvb_residual_add_dev(hid, dlt, H, s))
+        _ok(vv.vvb_lm_head_argmax_dev(hid, w, 1e-6, head, V, H, None, scr, sbytes, tok, None, s))
+
+    n0 = vv.launch_count()
+    ours(0, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    n_launch = vv.launch_count() - n0
+    us, us_min, mhz = time_graph(ours, 1, 5, clock)
+    res = {"case": "decode step, 28 layers, M=1 (row kernels + LM head only)", "config": None,
+           "us": round(us, 1), "min_us": round(us_min, 1), "launches": n_launch, "sm_mhz": mhz,
+           "incumbent_us": None, "incumbent_launches": None}
+
+    ref = load_reference_cuda()
+    if ref is not None and hasattr(ref, "vv_kv_store_dev"):
+        p = lambda t: t.data_ptr()
+        logits = torch.empty(V, device=dev, dtype=torch.float32)
+        sv, si = torch.empty(256, device=dev), torch.empty(256, device=dev, dtype=torch.int32)
+        count = [0]
+
+        def rk(st):
+            assert st == 0, st
+            count[0] += 1
+
+        def theirs(_i, s):
+            st = s.cuda_stream
+            rk(ref.vv_embedding_dev(p(table), p(tok), p(hid), 1, H, st))
+            for layer in range(L):
+                if layer:
+                    rk(ref.vv_residual_add_dev(p(hid), p(dlt), H, st))
+                rk(ref.vv_rmsnorm_dev(p(hid), p(w), p(nrm), 1, H, 1e-6, st))
+                rk(ref.vv_bias_add_dev(p(q1), p(bq), 1, NQ * HD, st))
+                rk(ref.vv_bias_add_dev(p(k1), p(bk), 1, NKV * HD, st))
+                rk(ref.vv_bias_add_dev(p(v1), p(bv), 1, NKV * HD, st))
+                rk(ref.vv_rope_dev(p(q1), 1, NQ, HD, 0, p(dpos), 1e6, st))
+                rk(ref.vv_rope_dev(p(k1), 1, NKV, HD, 0, p(dpos), 1e6, st))
+                rk(ref.vv_kv_store_dev(p(k1), p(v1), p(kc[layer]), p(vc[layer]), None, None, None, False,
+                                       NKV, HD, 0, p(dpos), 1, 0, None, st))
+                rk(ref.vv_residual_add_dev(p(hid), p(dlt), H, st))
+                rk(ref.vv_rmsnorm_dev(p(hid), p(w), p(nrm), 1, H, 1e-6, st))
+                rk(ref.vv_swiglu_dev(p(g1), p(u1), p(g1), INTER, st))
+            rk(ref.vv_residual_add_dev(p(hid), p(dlt), H, st))
+            rk(ref.vv_rmsnorm_dev(p(hid), p(w), p(nrm), 1, H, 1e-6, st))
+            rk(ref.vv_lm_head_gemv_dev(p(nrm), p(head), p(logits), V, H, st))
+            rk(ref.vv_argmax_dev(p(logits), V, p(sv), p(si), p(tok), None, st))
+
+        theirs(0, torch.cuda.current_stream())
+        torch.cuda.synchronize()
+        calls = count[0]
+        t_us, t_min, _ = time_graph(theirs, 1, 5)
+        res.update({"incumbent_us": round(t_us, 1), "incumbent_min_us": round(t_min, 1), "incumbent_calls": calls,
+                    "incumbent": "the reference's own CUDA kernels (release flags) in the engine's call order"})
+    return res
+
+
+def main(peak_gbs, peak_kind, only=None, plain=False):
+    print(json.dumps(run(peak_gbs, peak_kind, only, plain)), flush=True)

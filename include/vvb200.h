@@ -12,7 +12,9 @@
  * backend at link time:
  * include/vibevoice/device.h:11-14). The second group (vvb_*) is additive:
  * fused forms that save HBM passes, a host-buffer pipeline, and the row
- * partition used to shard tokens over the GPUs of one box.
+ * partition used to shard tokens over the GPUs of one box (the host-buffer
+ * pipeline and its multi-GPU form own streams, staging buffers and threads:
+ * they block and are not capturable, as their declarations say).
  *
  * Conventions (those of include/vibevoice/device.h:16-21):
  *   - every tensor pointer is caller-owned DEVICE memory of the current
@@ -27,7 +29,11 @@
  *     kernels that are not this library's), only launch latency overlaps;
  *     captured, a kernel-to-kernel dependency becomes a programmatic graph
  *     edge (CUDA 12.3 or later);
- *   - calls are re-entrant: no file-scope mutable state;
+ *   - calls are re-entrant: no file-scope mutable state. The one exception to
+ *     this and to the stream-capture rule above is vvb_lm_head_argmax_static_dev:
+ *     its calls share one array in the library image (calls that overlap on a
+ *     GPU race on it) and its first call per device looks that array's address
+ *     up, which belongs before any capture -- see its declaration;
  *   - the return value is a vv_status_t code; nothing throws, aborts or logs;
  *   - rows == 0 / n == 0 is VV_OK and launches nothing;
  *   - there is no CPU fallback anywhere: without a usable CUDA device the
@@ -403,6 +409,33 @@ void vvb_host_ctx_last_traffic(const vvb_host_ctx_t* ctx, uint64_t* h2d_bytes, u
  *  in milliseconds, from CUDA events recorded before its first upload and
  *  after its last download. */
 float vvb_host_ctx_last_ms(const vvb_host_ctx_t* ctx);
+
+/* ---- the same pipeline on several GPUs of one box ------------------------ */
+
+/** One vvb_host_ctx_t per device and a host thread to drive each. The
+ *  reference walks its devices from the host in the same way
+ *  (src/inference/pipeline.c:389-513, vv_dev_set_device at
+ *  src/cuda/cuda_utils.cu:301-325); rows are independent, so nothing is
+ *  exchanged between devices and no device reads another's memory.
+ *  `devices` lists the CUDA ordinals to use (NULL: 0 .. n_devices-1). */
+typedef struct vvb_host_multi vvb_host_multi_t;
+vv_status_t vvb_host_multi_create(vvb_host_multi_t** out, const int* devices, int n_devices,
+                                  int max_slice_rows, int hidden_size, int n_q_heads,
+                                  int n_kv_heads, int head_dim, int inter);
+void vvb_host_multi_destroy(vvb_host_multi_t* m);
+int vvb_host_multi_devices(const vvb_host_multi_t* m);
+
+/** vvb_layer_chain_host over all the context's devices: device g of n takes
+ *  the rows vvb_shard_rows(rows, n, g) gives it, with its first row added to
+ *  position_offset. Blocks until every shard is back in host memory; the
+ *  first failing shard's status is returned. Results are byte-identical to
+ *  the one-device call. */
+vv_status_t vvb_layer_chain_host_multi(vvb_host_multi_t* m, const vvb_layer_chain_t* host_tensors);
+
+/** Slowest device's device-side duration (ms) and the summed bytes moved by
+ *  the last vvb_layer_chain_host_multi call. */
+float vvb_host_multi_last_ms(const vvb_host_multi_t* m);
+void vvb_host_multi_last_traffic(const vvb_host_multi_t* m, uint64_t* h2d_bytes, uint64_t* d2h_bytes);
 
 /* ---- introspection ------------------------------------------------------ */
 

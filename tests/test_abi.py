@@ -52,7 +52,8 @@ def test_header_compiles_as_c11_and_cxx(tmp_path):
                     str(tmp_path / "t2.o")], check=True)
 
 
-REF_INCLUDE = os.environ.get("VV_REFERENCE_DIR", "/root/reference") + "/include"
+# the reference tree: VV_REFERENCE_DIR, else a directory named "reference" beside this repository
+REF_INCLUDE = os.environ.get("VV_REFERENCE_DIR", os.path.join(os.path.dirname(ROOT), "reference")) + "/include"
 
 
 @pytest.mark.skipif(not os.path.exists(REF_INCLUDE + "/vibevoice/device.h"), reason="reference headers not mounted")

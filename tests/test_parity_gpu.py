@@ -158,11 +158,10 @@ def test_config2_rope_prefill(vv, orc):
     assert np.array_equal(bits(host(q2)), bits(gq.get())) and np.array_equal(bits(host(k2)), bits(gk.get()))
 
 
-@pytest.mark.parametrize("rows", [64, 1024])
+@pytest.mark.parametrize("rows", [64, 4096])
 def test_config3_swiglu(vv, orc, rows):
-    """gate, up fp16 [rows, 18944] ~ N(0,1); the decode shape [64, 18944] and a
-    quarter of the prefill shape (the full [4096, 18944] runs in the property
-    tests below, where the oracle is not needed for every element)."""
+    """gate, up fp16 [rows, 18944] ~ N(0,1): the decode shape [64, 18944] and
+    the prefill shape [4096, 18944], every element against the oracle."""
     g = torch.Generator().manual_seed(0)
     gate = torch.randn(rows, 18944, generator=g).half().numpy()
     up = torch.randn(rows, 18944, generator=g).half().numpy()
@@ -203,27 +202,124 @@ def test_config4_embedding_rmsnorm(vv, orc):
     assert np.array_equal(bits(host(out)), bits(hid.get())) and np.array_equal(bits(host(out2)), bits(nor.get()))
 
 
-def test_config5_chain_slice(vv, orc):
-    """The layer chain at seed 1 on the tail of the 14449-token prompt (rows
-    14000..14448, where RoPE angles are largest)."""
-    T, first = 14449, 14000
-    rows = T - first
+def _histogram(name, d):
+    """0 / 1 / 2 / >2 ulp counts of a distance array, printed with the maximum."""
+    d = np.asarray(d)
+    counts = [int((d == 0).sum()), int((d == 1).sum()), int((d == 2).sum()), int((d > 2).sum())]
+    print(f"{name}: max {float(d.max()):.2f} ulp; elements at 0/1/2/>2 ulp: {counts}")
+    return counts
+
+
+def test_config5_chain_full(vv, orc):
+    """The layer chain at seed 1 over ALL T = 14449 rows, every element against
+    the oracle (which runs in row blocks to bound host memory)."""
+    T, H, NQ, NKV, HD, I = 14449, 3584, 28, 4, 128, 18944
     g = torch.Generator().manual_seed(1)
-    mk = lambda *s: torch.randn(*s, generator=g).half().numpy()
-    h, d = mk(rows, 3584), mk(rows, 3584)
-    w = (1 + 0.02 * torch.randn(3584, generator=g)).half().numpy()
-    q, k, gate, up = mk(rows, 28, 128), mk(rows, 4, 128), mk(rows, 18944), mk(rows, 18944)
-    dh, dn, dq, dk, dg = dev(h), torch.empty(rows, 3584, dtype=torch.float16, device="cuda"), dev(q), dev(k), dev(gate)
-    chain = vv.make_chain(dh, dev(d), dev(w), dn, dq, dk, dg, dev(up), rows, 3584, 28, 4, 128, 18944, first, 1e-6, 1e6)
+    mk = lambda *s: torch.randn(*s, generator=g).half()
+    h, d = mk(T, H), mk(T, H)
+    w = (1 + 0.02 * torch.randn(H, generator=g)).half()
+    q, k, gate, up = mk(T, NQ, HD), mk(T, NKV, HD), mk(T, I), mk(T, I)
+    dh, dd, dw, dq, dk, dg, du = (t.cuda() for t in (h, d, w, q, k, gate, up))
+    dn = torch.empty(T, H, dtype=torch.float16, device="cuda")
+    chain = vv.make_chain(dh, dd, dw, dn, dq, dk, dg, du, T, H, NQ, NKV, HD, I, 0, 1e-6, 1e6)
     n0 = vv.launch_count()
     assert vv.vvb_layer_chain_dev(chain) == 0
     assert vv.launch_count() - n0 == 1      # one grid carries all three operations
-    want_h, want_n = orc.add_rmsnorm_f16(h, d, w, 1e-6)
-    assert np.array_equal(bits(host(dh)), bits(want_h))
-    assert orc.ulp_distance(host(dn), want_n).max() <= NORM_ULP
-    assert orc.rope_error_in_ulps(host(dq), orc.rope_f16(q, first, 1e6), q).max() <= ROPE_ULP
-    assert orc.rope_error_in_ulps(host(dk), orc.rope_f16(k, first, 1e6), k).max() <= ROPE_ULP
-    assert orc.ulp_distance(host(dg), orc.swiglu_f16(gate, up)).max() <= SWIGLU_ULP
+    got_h, got_n, got_q, got_k, got_g = (host(t) for t in (dh, dn, dq, dk, dg))
+    del dh, dd, dq, dk, dg, du, dn
+    torch.cuda.empty_cache()
+    wn = w.numpy()
+    d_norm, d_swi, e_q, e_k, rope_bits = [], [], [], [], 0
+    for lo in range(0, T, 2048):
+        hi = min(T, lo + 2048)
+        want_h, want_n = orc.add_rmsnorm_f16(h[lo:hi].numpy(), d[lo:hi].numpy(), wn, 1e-6)
+        assert np.array_equal(bits(got_h[lo:hi]), bits(want_h))                  # updated hidden: bit-exact
+        d_norm.append(orc.ulp_distance(got_n[lo:hi], want_n).reshape(-1))
+        xq, xk = q[lo:hi].numpy(), k[lo:hi].numpy()
+        want_q, want_k = orc.rope_f16(xq, lo, 1e6), orc.rope_f16(xk, lo, 1e6)
+        e_q.append(orc.rope_error_in_ulps(got_q[lo:hi], want_q, xq).reshape(-1))
+        e_k.append(orc.rope_error_in_ulps(got_k[lo:hi], want_k, xk).reshape(-1))
+        rope_bits += int((bits(got_q[lo:hi]) != bits(want_q)).sum() + (bits(got_k[lo:hi]) != bits(want_k)).sum())
+        want_g = orc.swiglu_f16(gate[lo:hi].numpy(), up[lo:hi].numpy())
+        d_swi.append(orc.ulp_distance(got_g[lo:hi], want_g).reshape(-1))
+    d_norm, d_swi, e_q, e_k = (np.concatenate(x) for x in (d_norm, d_swi, e_q, e_k))
+    _histogram("config 5 normed", d_norm)
+    _histogram("config 5 swiglu", d_swi)
+    print(f"config 5 rope: max error {max(e_q.max(), e_k.max()):.3f} fp16 ulp at operand scale; "
+          f"{rope_bits} of {e_q.size + e_k.size} elements differ in bits")
+    assert d_norm.max() <= NORM_ULP and d_norm.max() <= 1
+    assert d_swi.max() <= SWIGLU_ULP and d_swi.max() <= 1 and (d_swi > 0).mean() < 5e-3
+    assert e_q.max() <= ROPE_ULP and e_k.max() <= ROPE_ULP
+    assert rope_bits < 1e-4 * (e_q.size + e_k.size)
+
+
+def test_two_gpu_shards_reassemble(vv):
+    """Shards g = 0, 1 of the 14449-row chain on devices 0 and 1 (vvb_shard_rows,
+    the shard's first row as RoPE's position offset): the reassembled bytes are
+    those of the one-GPU run. No peer access: each device sees only its rows."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two visible GPUs")
+    T, H, NQ, NKV, HD, I = 14449, 3584, 28, 4, 128, 18944
+    g = torch.Generator().manual_seed(1)
+    mk = lambda *s: torch.randn(*s, generator=g).half()
+    h, d = mk(T, H), mk(T, H)
+    w = (1 + 0.02 * torch.randn(H, generator=g)).half()
+    q, k, gate, up = mk(T, NQ, HD), mk(T, NKV, HD), mk(T, I), mk(T, I)
+
+    def run_on(device, first, rows):
+        with torch.cuda.device(device):
+            sl = slice(first, first + rows)
+            t = [x[sl].to(f"cuda:{device}") for x in (h, d, q, k, gate, up)]
+            dw = w.to(f"cuda:{device}")
+            dn = torch.empty(rows, H, dtype=torch.float16, device=f"cuda:{device}")
+            chain = vv.make_chain(t[0], t[1], dw, dn, t[2], t[3], t[4], t[5], rows, H, NQ, NKV, HD, I, first, 1e-6, 1e6)
+            assert vv.vvb_layer_chain_dev(chain) == 0
+            torch.cuda.synchronize(device)
+            return [x.cpu() for x in (t[0], dn, t[2], t[3], t[4])]
+
+    whole = run_on(0, 0, T)
+    parts = [run_on(dev_i, *vv.vvb_shard_rows(T, 2, dev_i)) for dev_i in (0, 1)]
+    assert sum(p[0].shape[0] for p in parts) == T
+    for i, name in enumerate(("hidden", "normed", "q", "k", "swiglu")):
+        joined = torch.cat([p[i] for p in parts])
+        assert torch.equal(joined.view(torch.int16), whole[i].view(torch.int16)), name
+    torch.cuda.set_device(0)
+
+
+def test_norm_sum_stress_rows(vv, orc):
+    """Rows built to stress the sum of squares: one huge element among thousands
+    of tiny ones, alternating magnitudes, subnormal halves, all-equal and zero
+    rows -- the normalised rows (and the int8 rows made from them) must still be
+    the oracle's, whose sum runs in double."""
+    H = 3584
+    rng = np.random.default_rng(77)
+    rows = []
+    r = (rng.standard_normal(H) * 1e-3).astype(np.float16); r[17] = np.float16(60000.0); rows.append(r)
+    r = (rng.standard_normal(H) * 6e-5).astype(np.float16); r[H - 1] = np.float16(-65504.0); rows.append(r)
+    r = np.where(np.arange(H) % 2 == 0, 1000.0, 1e-4).astype(np.float16) * rng.choice([-1, 1], H).astype(np.float16)
+    rows.append(r)
+    rows.append(np.full(H, 6e-8, np.float16))                       # subnormal halves only
+    rows.append(np.full(H, 255.0, np.float16))
+    rows.append(np.zeros(H, np.float16))
+    r = (2.0 ** rng.integers(-20, 15, H)).astype(np.float16) * rng.choice([-1, 1], H).astype(np.float16); rows.append(r)
+    r = rng.standard_normal(H).astype(np.float16); r[::97] = np.float16(30000.0); rows.append(r)
+    x = np.stack(rows)
+    # many copies, so that both launch shapes (one wave, deep grid) see them
+    for reps in (1, 200):
+        xx = np.ascontiguousarray(np.tile(x, (reps, 1)))
+        w = (1 + 0.02 * rng.standard_normal(H)).astype(np.float16)
+        _, want = orc.add_rmsnorm_f16(xx, None, w, 1e-6)
+        out = Guarded(np.zeros_like(xx))
+        assert vv.vv_rmsnorm_dev(dev(xx), dev(w), out.ptr, xx.shape[0], H, 1e-6) == 0
+        got = out.get()
+        assert orc.ulp_distance(got, want).max() == 0, "the double sum decides these rows; bits must agree"
+        for layout in (0, 3):
+            xq = torch.empty(xx.shape[0], H, dtype=torch.int8, device="cuda")
+            sx = torch.empty(xx.shape[0], dtype=torch.float32, device="cuda")
+            xs = torch.empty(xx.shape[0], H // 32, dtype=torch.int32, device="cuda")
+            assert vv.vv_rmsnorm_q8_dev(dev(xx), dev(w), xx.shape[0], H, 1e-6, layout, xq, sx, xs) == 0
+            wq, wsx, wxs = orc.restated().quant_act_q8(want.astype(np.float32), layout)
+            assert np.array_equal(host(xq), wq) and np.array_equal(host(sx), wsx) and np.array_equal(host(xs), wxs)
 
 
 @pytest.mark.parametrize("rows,H,nq,nkv,hd,inter,expect_launches", [

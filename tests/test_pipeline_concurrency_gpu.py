@@ -139,3 +139,39 @@ def test_chain_replays_under_a_cuda_graph(vv):
         torch.cuda.synchronize()
         for key, val in (("h", dv["h"]), ("n", n), ("q", dv["q"]), ("k", dv["k"]), ("gate", dv["gate"])):
             assert torch.equal(val.cpu().view(torch.int16), want[key].view(torch.int16)), key
+
+
+@pytest.mark.parametrize("rows,devices", [(1000, [0, 0, 0]), (5, [0, 0, 0, 0, 0, 0, 0, 0]), (2500, [0, 1]), (0, [0, 0])])
+def test_host_multi_matches_one_device(vv, rows, devices):
+    """vvb_layer_chain_host_multi: one pipeline and one host thread per listed
+    device, rows sharded by vvb_shard_rows with the shard's first row as RoPE's
+    offset; the bytes are those of the one-device path. Listing a device more
+    than once puts several pipelines on it (which exercises the sharding and the
+    threads on a single GPU); [0, 1] needs two GPUs. More devices than rows
+    leaves the last shards empty."""
+    if max(devices) >= torch.cuda.device_count():
+        pytest.skip("needs more visible GPUs")
+    first = 77
+    t = make_inputs(max(rows, 1), rows + 3)
+    if rows == 0:
+        t = {k: (v[:0] if k != "w" else v) for k, v in t.items()}
+    want = run_on_device(vv, t, rows, first) if rows else None
+    pin = {k: v.clone().pin_memory() for k, v in t.items()}
+    n = torch.empty(rows, H, dtype=torch.float16).pin_memory()
+    pipe = vv.HostPipelineMulti(devices, 256, H, NQ, NKV, HD, INTER)
+    assert pipe.devices() == len(devices)
+    c = vv.make_chain(pin["h"], pin["d"], pin["w"], n, pin["q"], pin["k"], pin["gate"], pin["up"], rows, H, NQ, NKV,
+                      HD, INTER, first, 1e-6, 1e6)
+    for _ in range(2):                                       # a context is reusable
+        for k in ("h", "q", "k", "gate"):
+            pin[k].copy_(t[k])
+        assert pipe.run(c) == 0
+        if rows:
+            for got, key in ((pin["h"], "h"), (n, "n"), (pin["q"], "q"), (pin["k"], "k"), (pin["gate"], "gate")):
+                assert torch.equal(got.view(torch.int16), want[key].view(torch.int16)), key
+    h2d, d2h = pipe.last_traffic()
+    assert d2h == rows * 2 * (2 * H + (NQ + NKV) * HD + INTER)
+    busy = sum(1 for g in range(len(devices)) if vv.vvb_shard_rows(rows, len(devices), g)[1] > 0)
+    assert h2d == rows * 2 * (2 * H + (NQ + NKV) * HD + 2 * INTER) + 2 * H * busy   # gamma goes to every device with rows
+    pipe.close()
+    torch.cuda.set_device(0)

@@ -112,8 +112,10 @@ def test_act_quant_golden(vv, q8gold, K, layout):
 
 
 @gpu
-@pytest.mark.parametrize("M", [1, 7, 285])
-@pytest.mark.parametrize("K", [1536, 3584, 8960, 18944])
+@pytest.mark.parametrize("M,K", [(m, k) for m in (1, 7, 285) for k in (1536, 3584, 8960, 18944)] +
+                         # deep grids (more rows than one wave): the two-warps-per-row instances for every
+                         # width they serve, and widths either side of them that take the general shape
+                         [(700, k) for k in (1024, 1536, 2048, 2560, 3072, 3584, 4096, 4608, 3616, 18944)])
 def test_q8_kernels_equal_oracle_and_unfused(vv, orc, M, K):
     """The shapes of tests/test_int8_linear.c:295-354. Each fused quantizer is
     bit-identical (a) to the CPU quantizer applied to the FP16 values the

@@ -36,7 +36,7 @@ PROGRAMS = ["test_int8_linear", "test_decode_position", "test_prefill_append", "
 
 
 @pytest.mark.parametrize("name", PROGRAMS)
-def test_reference_program_passes_on_this_library(name):
+def test_reference_program_passes_on_this_library(name, tmp_path):
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     exe = os.path.join(BIN, name)
@@ -44,10 +44,7 @@ def test_reference_program_passes_on_this_library(name):
         pytest.skip(f"{name} was not built (oracle/build_reftests.sh needs the reference's sources)")
     r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     out = r.stdout + r.stderr
-    log_dir = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(log_dir):
-        with open(os.path.join(log_dir, f"reference_{name}.log"), "w") as fh:
-            fh.write(out)
+    (tmp_path / f"reference_{name}.log").write_text(out)
     tail = "\n".join(out.splitlines()[-25:])
     assert r.returncode == 0, tail
     # a program that found no device reports a skip and exits 0: that is not a pass

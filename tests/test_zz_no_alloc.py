@@ -29,7 +29,7 @@ def vv():
     return vvb200
 
 
-def run_both(vv, V, K, seed, planted):
+def run_both(vv, V, K, seed, planted, device_memory_must_not_move):
     g = torch.Generator(device="cuda").manual_seed(seed)
     h = (3 * torch.randn(K, generator=g, device="cuda")).half()
     gamma = (1 + 0.1 * torch.randn(K, generator=g, device="cuda")).half()
@@ -46,10 +46,19 @@ def run_both(vv, V, K, seed, planted):
     lg = torch.empty(V, dtype=torch.float32, device="cuda")
     tok = torch.full((1,), -1, dtype=torch.int32, device="cuda")
     val = torch.zeros(1, dtype=torch.float32, device="cuda")
+    # torch's own counter sees only torch's allocator; the free bytes the driver reports
+    # (cudaMemGetInfo) also move for a cudaMalloc or cudaMallocAsync made inside the library.
+    # The very first call on a device may load the library's module lazily, which takes device
+    # memory once, so the driver's figure is held still from the second call on.
+    torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
+    free_before, _ = torch.cuda.mem_get_info()
     assert vv.vvb_lm_head_argmax_static_dev(h, gamma, 1e-6, w, V, K, lg, tok, val) == vv.VV_OK
     torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
     assert torch.cuda.memory_allocated() == before
+    if device_memory_must_not_move:
+        assert free_after == free_before, (free_before, free_after)
     assert int(tok.item()) == int(tok_ref.item()) == planted
     assert torch.equal(val.view(torch.int32), val_ref.view(torch.int32))
     assert torch.equal(lg.view(torch.int32), lg_ref.view(torch.int32))
@@ -58,9 +67,11 @@ def run_both(vv, V, K, seed, planted):
 
 def test_static_scratch_entry_point_matches_the_caller_scratch_one_twice_in_a_row(vv):
     # first call: the 7B model's head, 152064 rows of 3584
-    assert run_both(vv, 152064, 3584, seed=11, planted=150001) == 150001
+    assert run_both(vv, 152064, 3584, seed=11, planted=150001, device_memory_must_not_move=False) == 150001
     # second call straight after, a much shorter head: the array still holds the first call's partials
-    assert run_both(vv, 4000, 1536, seed=12, planted=17) == 17
+    assert run_both(vv, 4000, 1536, seed=12, planted=17, device_memory_must_not_move=True) == 17
+    # and a third, back at the full head
+    assert run_both(vv, 152064, 3584, seed=13, planted=9, device_memory_must_not_move=True) == 9
 
 
 def test_static_scratch_entry_point_limits_and_errors(vv):

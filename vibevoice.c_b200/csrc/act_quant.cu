@@ -33,6 +33,24 @@ extern std::atomic<uint64_t> g_launches;
 
 enum { Q_PLAIN = 0, Q_RMSNORM = 1, Q_SWIGLU = 2 };
 
+/* Deep grids of rows that split into whole vectors over 64 threads (hidden
+ * sizes 1536 .. 4096 in steps of 512: 3 .. 8 vectors per thread) run as TWO
+ * WARPS PER ROW. These kernels are bound by instruction issue and by the
+ * latency of their per-row reductions, not by HBM; two warps per row keep 12
+ * rows resident per SM instead of 8, put no thread on padding (128 threads x 4
+ * vectors leave an eighth of a 3584-wide row's slots empty) and halve the
+ * cross-warp part of both reductions. Measured at [14449, 3584]: rmsnorm_q8
+ * 40.3 us against 49.1 us for 128 x 4 (45.2 against 52.0 in the weight-GEMM
+ * layout), act_quant 22.3 against 26.3; 224 threads x 2 vectors, the other
+ * padding-free shape, is slower than both (55 us). */
+constexpr int kTwoWarpThreads = 64;
+constexpr int kTwoWarpMinB = 12;          /* CTAs per SM: 80 registers per thread */
+static inline int two_warp_vpt(int rows, int nvec, int mode) {
+    if (mode == 2 || rows <= kLatencyRows || nvec % kTwoWarpThreads != 0) return 0;
+    const int v = nvec / kTwoWarpThreads;
+    return (v >= 3 && v <= 8) ? v : 0;
+}
+
 struct ActQuantArgs {
     RowNormArgs norm;        /* Q_RMSNORM: src/delta/row_out/weight/eps; normed unused */
     const vec16* a;          /* Q_PLAIN: x;  Q_SWIGLU: gate */
@@ -63,8 +81,16 @@ __device__ __forceinline__ uint32_t transpose4(uint32_t v, int i) {
     return (i & 1) ? __byte_perm(y, v, 0x7351) : __byte_perm(v, y, 0x6240);
 }
 
-template <int VPT, int MODE>
-__global__ void __launch_bounds__(1024)
+/* MAXT: the largest CTA an instance is launched with; MINB: CTAs per SM it is
+ * compiled for, i.e. a register budget of 65536 / (MAXT * MINB). These kernels
+ * alternate loads, two CTA-wide reductions and a long arithmetic tail, and they
+ * live on warps in flight: an instance that takes 38 registers instead of 32
+ * loses a resident CTA per SM and with it 10-18 % (measured: swiglu_q8 297 us
+ * against 252 us at 14449 rows, the 512-row norm 3.4 us against 2.7 us because
+ * its 512 CTAs then need two waves), so the budget is stated, not left to the
+ * compiler. GUARD: how much of the inside-the-row test it carries (row_norm.cuh). */
+template <int VPT, int MODE, int GUARD, int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB)
 act_quant_kernel(const ActQuantArgs a) {
     pdl_wait();
     pdl_trigger();
@@ -72,18 +98,20 @@ act_quant_kernel(const ActQuantArgs a) {
     const int t = threadIdx.x, G = blockDim.x;
     const int row = blockIdx.x;
     const size_t roff = (size_t)row * (size_t)a.nvec;
+#define VVB_Q_IN(j) vec_inside<VPT, GUARD>(j, t + (j) * G, a.nvec)
 
     /* 1. the FP16 row the unfused op would write, in registers */
     vec16 yv[VPT];
     if (MODE == Q_RMSNORM) {
-        row_norm_produce<VPT, 1>(a.norm, row, t, G, 0, yv);
+        row_norm_produce<VPT, 1, GUARD, (VPT > 4)>(a.norm, row, t, G, 0, yv);
     } else {
         vec16 bv[VPT];
+        const vec16* ap = a.a + roff + t;
+        const vec16* bp = a.b + roff + t;
 #pragma unroll
         for (int j = 0; j < VPT; j++) {
-            const int v = t + j * G;
-            yv[j] = (v < a.nvec) ? ld_stream(a.a + roff + v) : make_uint4(0, 0, 0, 0);
-            if (MODE == Q_SWIGLU) bv[j] = (v < a.nvec) ? ld_stream(a.b + roff + v) : make_uint4(0, 0, 0, 0);
+            yv[j] = VVB_Q_IN(j) ? ld_stream(ap + j * G) : make_uint4(0, 0, 0, 0);
+            if (MODE == Q_SWIGLU) bv[j] = VVB_Q_IN(j) ? ld_stream(bp + j * G) : make_uint4(0, 0, 0, 0);
         }
         if (MODE == Q_SWIGLU) {
 #pragma unroll
@@ -106,8 +134,11 @@ act_quant_kernel(const ActQuantArgs a) {
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if ((t & 31) == 0) red_max[t >> 5] = amax;
     __syncthreads();
-    amax = 0.0f;
-    for (int w = 0; w < (G >> 5); w++) amax = fmaxf(amax, red_max[w]);
+    /* every lane folds the per-warp maxima with one shared-memory read and a
+     * shuffle tree (G <= 1024: at most 32 warps) */
+    amax = ((t & 31) < (G >> 5)) ? red_max[t & 31] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
 
     const float inv = (amax > 0.0f) ? __fdiv_rn(127.0f, amax) : 0.0f;
     if (t == 0) a.sx[row] = __fdiv_rn(amax, 127.0f);
@@ -122,7 +153,7 @@ act_quant_kernel(const ActQuantArgs a) {
 #pragma unroll
     for (int j = 0; j < VPT; j++) {
         const int v = t + j * G;
-        const bool ok = v < a.nvec;
+        const bool ok = VVB_Q_IN(j);
         /* round-half-even without the conversion unit: p = v*inv is rounded
          * to float first (as the CPU does) and adding 1.5*2^23 rounds it to an
          * integer in the float adder's nearest-even mode; the low byte of the
@@ -252,14 +283,59 @@ col_absmax_scalar_kernel(const __half* __restrict__ x, int M, int K, float* __re
     if (v == v) atomicMax(reinterpret_cast<int*>(acc) + k, __float_as_int(v));
 }
 
+/* Register budgets (see act_quant_kernel): the instances that must take any CTA
+ * size get 32 registers (two 1024-thread CTAs per SM) unless they hold a norm
+ * row of two or four vectors per thread; the instances for CTAs of at most 256
+ * threads get 32 registers too (eight CTAs per SM) when they are light, and 64
+ * (four CTAs) when they carry the norm. */
+constexpr int q_minb_any(int vpt, int mode) { return (mode == Q_RMSNORM && vpt > 1) ? 1 : 2; }
+constexpr int q_minb_256(int mode) { return mode == Q_RMSNORM ? 4 : 8; }
+
+template <int VPT, int MODE>
+static void launch_two_warp(const ActQuantArgs& a, cudaStream_t s) {
+    launch_pdl(act_quant_kernel<VPT, MODE, GUARD_NONE, kTwoWarpThreads, kTwoWarpMinB>, dim3(a.rows),
+               dim3(kTwoWarpThreads), 0, s, a);
+}
+
+template <int VPT, int MODE>
+static void launch_q_vpt(const ActQuantArgs& a, int threads, cudaStream_t s) {
+    const int guard = threads <= 256 ? row_guard_mode(a.nvec, threads, VPT) : GUARD_ALL;
+    const dim3 grid(a.rows), block(threads);
+    if (guard == GUARD_NONE)
+        launch_pdl(act_quant_kernel<VPT, MODE, GUARD_NONE, 256, q_minb_256(MODE)>, grid, block, 0, s, a);
+    else if (guard == GUARD_LAST)
+        launch_pdl(act_quant_kernel<VPT, MODE, GUARD_LAST, 256, q_minb_256(MODE)>, grid, block, 0, s, a);
+    else
+        launch_pdl(act_quant_kernel<VPT, MODE, GUARD_ALL, 1024, q_minb_any(VPT, MODE)>, grid, block, 0, s, a);
+}
+
 template <int MODE>
 static cudaError_t launch_q(const ActQuantArgs& a, cudaStream_t s) {
+    if (MODE != Q_SWIGLU) {
+        bool done = true;
+        switch (two_warp_vpt(a.rows, a.nvec, MODE)) {
+            case 3: launch_two_warp<3, MODE>(a, s); break;
+            case 4: launch_two_warp<4, MODE>(a, s); break;
+            case 5: launch_two_warp<5, MODE>(a, s); break;
+            case 6: launch_two_warp<6, MODE>(a, s); break;
+            case 7: launch_two_warp<7, MODE>(a, s); break;
+            case 8: launch_two_warp<8, MODE>(a, s); break;
+            default: done = false;
+        }
+        if (done) {
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            return cudaGetLastError();
+        }
+    }
     int threads, vpt;
     row_launch_shape(a.rows, a.nvec, &threads, &vpt);
     switch (vpt) {
-        case 1: launch_pdl(act_quant_kernel<1, MODE>, dim3(a.rows), dim3(threads), 0, s, a); break;
-        case 2: launch_pdl(act_quant_kernel<2, MODE>, dim3(a.rows), dim3(threads), 0, s, a); break;
-        case 4: launch_pdl(act_quant_kernel<4, MODE>, dim3(a.rows), dim3(threads), 0, s, a); break;
+        case 1:
+            launch_pdl(act_quant_kernel<1, MODE, GUARD_ALL, 1024, q_minb_any(1, MODE)>, dim3(a.rows), dim3(threads), 0,
+                       s, a);
+            break;
+        case 2: launch_q_vpt<2, MODE>(a, threads, s); break;
+        case 4: launch_q_vpt<4, MODE>(a, threads, s); break;
         default: return cudaErrorInvalidValue;
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -286,8 +362,7 @@ extern "C" int vvbk_act_quant(int mode, const void* a, const void* b, const void
     q.rows = M;
     q.nvec = K / 8;
     q.layout = layout;
-    q.norm = RowNormArgs{(const vec16*)a, (const vec16*)b, nullptr, (vec16*)row_out, (const vec16*)weight,
-                         nullptr, M, K / 8, K, 0, eps};
+    q.norm = make_row_norm_args(a, b, nullptr, row_out, weight, nullptr, M, K, 0, eps);
     if (mode == Q_RMSNORM) return (int)launch_q<Q_RMSNORM>(q, s);
     if (mode == Q_SWIGLU) return (int)launch_q<Q_SWIGLU>(q, s);
     return (int)launch_q<Q_PLAIN>(q, s);

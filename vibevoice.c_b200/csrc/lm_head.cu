@@ -244,15 +244,37 @@ using namespace vvb;
 /* Upper bound on the number of CTAs (= argmax partials) a launch over V rows uses. */
 extern "C" int vvbk_lm_head_partials(int V) { return (V + kLmMinRowsPerCta - 1) / kLmMinRowsPerCta; }
 
+/* CTAs of lm_head_kernel<NORM> resident at once on the current device for
+ * `smem` bytes of dynamic shared memory. The answer is cached per host thread
+ * (keyed by device, variant and size), so the one-row decode path -- where
+ * this launch is latency-sensitive and runs once per token -- makes no runtime
+ * query after its first call. A query that fails falls back to one CTA per SM
+ * of a 148-SM part and clears the runtime's last-error slot, so that the
+ * launch that follows is not reported as failed. */
 template <bool NORM>
 static int lm_head_resident_ctas(size_t smem) {
-    int dev = 0, sms = 148, per_sm = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    static thread_local int c_dev = -1, c_ctas = 0;
+    static thread_local size_t c_smem = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 148;
+    }
+    if (dev == c_dev && smem == c_smem && c_ctas > 0) return c_ctas;
+    int sms = 148, per_sm = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+        (void)cudaGetLastError();
+        sms = 148;
+    }
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lm_head_kernel<NORM>, kLmThreads, smem) != cudaSuccess ||
-        per_sm < 1)
+        per_sm < 1) {
+        (void)cudaGetLastError();
         per_sm = 1;
-    return sms * per_sm;
+    }
+    c_dev = dev;
+    c_smem = smem;
+    c_ctas = sms * per_sm;
+    return c_ctas;
 }
 
 /* logits (may be NULL) and/or per-CTA argmax partials (part_v/part_i, may be
@@ -325,7 +347,10 @@ extern "C" int vvbk_argmax_reduce(const float* part_v, const int* part_i, int n,
  * device address, so the address is looked up with cudaGetSymbolAddress -- once
  * per device, by the first call made while that device is current, and kept in
  * a table indexed by device. That first call talks to the runtime beyond a
- * plain launch, so make it during start-up, before any stream capture.
+ * plain launch, so make it during start-up, before any stream capture. The
+ * table is never refreshed: the library must not be kept across a
+ * cudaDeviceReset (or any other teardown of the device's primary context),
+ * after which the array lives at an address the table no longer knows.
  *
  * Every call on a device writes into the one array. Nothing in it has to
  * start at zero (each launch overwrites exactly the entries its reduce step

@@ -34,9 +34,6 @@
 #include "rope.cuh"
 
 #include <atomic>
-#ifdef VVB_TUNING
-#include <cstdlib>
-#endif
 
 /* CTAs per SM the tile kernel is compiled for: 3 (75 registers, no spills)
  * measures 36.5 us at 14449 rows and 11.9 at 4096 against 36.9 and 12.1 at 4
@@ -106,10 +103,7 @@ extern "C" int vvbk_rope(void* q, void* k, int rows, int n_q_heads, int n_kv_hea
 
     if (head_dim % 16 == 0 && aligned16(q) && aligned16(k)) {
         RopeArgs a;
-        int max_passes = kRopeMaxRowsPerThread;
-#ifdef VVB_TUNING
-        if (const char* e = getenv("VVB_TUNE_ROPE_PASSES")) { int p = atoi(e); if (p >= 1 && p < max_passes) max_passes = p; }
-#endif
+        const int max_passes = kRopeMaxRowsPerThread;
         unsigned gx, gy;
         rope_plan(a, q, k, rows, n_q_heads, n_kv_heads, head_dim, position_offset, d_position, inv_freq,
                   max_passes, &gx, &gy);

@@ -68,7 +68,9 @@ __device__ __forceinline__ void sincos_f64(float angle, float* s_out, float* c_o
     *c_out = ((q + 1) & 2) ? -c1 : c1;
 }
 
-/* One CTA's tile: block (bx, by) of the (row tiles, column chunks) grid. */
+/* One CTA's tile: block (bx, by) of the (row tiles, column chunks) grid; THREADS
+ * is the CTA size the plan was made for (rope_plan's `threads`). */
+template <int THREADS = kRopeThreads>
 __device__ __forceinline__ void rope_tile_body(const RopeArgs& a, int bx, int by) {
     __shared__ __align__(16) float cos_s[kRopeTableEntries];
     __shared__ __align__(16) float sin_s[kRopeTableEntries];
@@ -81,7 +83,7 @@ __device__ __forceinline__ void rope_tile_body(const RopeArgs& a, int bx, int by
     /* This thread's column, fixed for all its rows. */
     const int slot = t / a.cols_per_cta;
     const int cl = t - slot * a.cols_per_cta;
-    const int c = by * kRopeThreads + cl;
+    const int c = by * THREADS + cl;
     const bool col_ok = (slot < a.row_slots) && (c < a.items_per_row);
     const int head = c / a.hvn;
     const int vec = c - head * a.hvn;
@@ -113,7 +115,7 @@ __device__ __forceinline__ void rope_tile_body(const RopeArgs& a, int bx, int by
 
     /* Phase B: the CTA's cos/sin, once per (row, frequency). */
     const int pos0 = (a.d_position != nullptr ? *a.d_position : a.position_offset) + row0;
-    for (int e = t; e < nrows * a.half; e += kRopeThreads) {
+    for (int e = t; e < nrows * a.half; e += THREADS) {
         const int rl = e / a.half;
         const int i = e - rl * a.half;
         const float ang = __fmul_rn((float)(pos0 + rl), a.inv_freq[i]);
@@ -148,7 +150,8 @@ __device__ __forceinline__ void rope_tile_body(const RopeArgs& a, int bx, int by
  * problem (head_dim a multiple of 16) and return the (x, y) grid. */
 static inline void rope_plan(RopeArgs& a, void* q, void* k, int rows, int n_q_heads, int n_kv_heads,
                              int head_dim, int position_offset, const int* d_position,
-                             const float* inv_freq, int max_passes, unsigned* gx, unsigned* gy) {
+                             const float* inv_freq, int max_passes, unsigned* gx, unsigned* gy,
+                             int threads = kRopeThreads) {
     const int half = head_dim / 2;
     a.q = (vec16*)q;
     a.k = (vec16*)k;
@@ -161,8 +164,8 @@ static inline void rope_plan(RopeArgs& a, void* q, void* k, int rows, int n_q_he
     a.items_per_row = (n_q_heads + n_kv_heads) * a.hvn;
     a.position_offset = position_offset;
     for (int i = 0; i < half; i++) a.inv_freq[i] = inv_freq[i];
-    a.cols_per_cta = a.items_per_row < kRopeThreads ? a.items_per_row : kRopeThreads;
-    a.row_slots = kRopeThreads / a.cols_per_cta;
+    a.cols_per_cta = a.items_per_row < threads ? a.items_per_row : threads;
+    a.row_slots = threads / a.cols_per_cta;
     /* rows per CTA = row_slots * passes, bounded by the cos/sin table */
     int passes = kRopeTableEntries / (half * a.row_slots);
     if (passes > max_passes) passes = max_passes;
@@ -175,7 +178,7 @@ static inline void rope_plan(RopeArgs& a, void* q, void* k, int rows, int n_q_he
      * is a latency problem instead: it takes the fewest rows per thread that
      * still fit one wave (1.86 against 2.48 us at 64 rows, 4.43 against 5.08 at
      * 1024). kRopeOneWave = 3 CTAs on each of 148 SMs. */
-    const unsigned gy_ = (unsigned)((a.items_per_row + kRopeThreads - 1) / kRopeThreads);
+    const unsigned gy_ = (unsigned)((a.items_per_row + threads - 1) / threads);
     for (int p = 1; p < passes; p++) {
         const unsigned ctas = (unsigned)((rows + a.row_slots * p - 1) / (a.row_slots * p)) * gy_;
         if (ctas <= kRopeOneWave) { passes = p; break; }

@@ -33,21 +33,23 @@
 #include "vvb_launch.h"
 
 #include <atomic>
-#ifdef VVB_TUNING
-#include <cstdlib>
-#endif
 
 namespace vvb {
 
 extern std::atomic<uint64_t> g_launches;
 
 /* ----------------------------------------------------------------- CTA/row */
-template <int VPT>
-__global__ void __launch_bounds__(1024)
+/* MAXT: the largest CTA the instance is launched with; MINB: CTAs per SM it is
+ * compiled for (a register budget of 65536 / (MAXT * MINB)). The one-vector
+ * instance serves the grids of at most one wave, and "one wave" (kLatencyRows)
+ * counts four 448-thread CTAs per SM, which needs 32 registers: at 37 the 512
+ * rows of a short prefill take two waves and 3.4 us instead of 2.7 us. */
+template <int VPT, int GUARD, int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB)
 row_norm_cta_kernel(const RowNormArgs a) {
     pdl_wait();
     pdl_trigger();
-    row_norm_body<VPT, 1>(a, blockIdx.x, threadIdx.x, blockDim.x, 0);
+    row_norm_body<VPT, 1, GUARD>(a, blockIdx.x, threadIdx.x, blockDim.x, 0);
 }
 
 /* ----------------------------------------------------------------- generic */
@@ -159,11 +161,20 @@ static int sm_count() {
     return cached_sms;
 }
 
+template <int VPT>
+static void launch_cta_vpt(const RowNormArgs& a, int threads, cudaStream_t s) {
+    const int guard = threads <= 256 ? row_guard_mode(a.nvec, threads, VPT) : GUARD_ALL;
+    const dim3 grid(a.rows), block(threads);
+    if (guard == GUARD_NONE) launch_pdl(row_norm_cta_kernel<VPT, GUARD_NONE, 256, 4>, grid, block, 0, s, a);
+    else if (guard == GUARD_LAST) launch_pdl(row_norm_cta_kernel<VPT, GUARD_LAST, 256, 4>, grid, block, 0, s, a);
+    else launch_pdl(row_norm_cta_kernel<VPT, GUARD_ALL, 1024, 1>, grid, block, 0, s, a);
+}
+
 static cudaError_t launch_cta(const RowNormArgs& a, int vpt, int threads, cudaStream_t s) {
     switch (vpt) {
-        case 1: launch_pdl(row_norm_cta_kernel<1>, dim3(a.rows), dim3(threads), 0, s, a); break;
-        case 2: launch_pdl(row_norm_cta_kernel<2>, dim3(a.rows), dim3(threads), 0, s, a); break;
-        case 4: launch_pdl(row_norm_cta_kernel<4>, dim3(a.rows), dim3(threads), 0, s, a); break;
+        case 1: launch_pdl(row_norm_cta_kernel<1, GUARD_ALL, 1024, 2>, dim3(a.rows), dim3(threads), 0, s, a); break;
+        case 2: launch_cta_vpt<2>(a, threads, s); break;
+        case 4: launch_cta_vpt<4>(a, threads, s); break;
         default: return cudaErrorInvalidValue;
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -206,8 +217,7 @@ extern "C" int vvbk_row_norm(const void* src_rows, const void* delta, const int3
     }
 
     if (vec_ok && nvec <= 4096) {
-        RowNormArgs a{(const vec16*)src_rows, (const vec16*)delta, ids, (vec16*)row_out,
-                      (const vec16*)weight, (vec16*)normed, rows, nvec, hidden, vocab, eps};
+        const RowNormArgs a = make_row_norm_args(src_rows, delta, ids, row_out, weight, normed, rows, hidden, vocab, eps);
         /* A quarter of the row's vectors per thread (128 threads x 4 for a
          * 3584-wide row) is fastest once the grid is several waves deep
          * (62.2 us against 63.4 and 81.7 for 2 and 1 at 14449 rows). Up to a
@@ -216,12 +226,6 @@ extern "C" int vvbk_row_norm(const void* src_rows, const void* delta, const int3
          * 2.06 us at one row (the decode shape), 4.27 against 4.55 at 512. */
         int threads, vpt;
         row_launch_shape(rows, nvec, &threads, &vpt);
-#ifdef VVB_TUNING
-        if (const char* e = getenv("VVB_TUNE_ROWNORM_VPT")) {
-            vpt = atoi(e);
-            threads = round_up_warp((nvec + vpt - 1) / vpt);
-        }
-#endif
         return (int)launch_cta(a, vpt, threads, s);
     }
 

@@ -28,10 +28,6 @@
 #include "vvb_launch.h"
 
 #include <atomic>
-#ifdef VVB_TUNING
-#include <cstdlib>
-extern "C" int vvbk_swiglu_bulk(const void* gate, const void* up, void* out, size_t nvec, void* stream, int variant);
-#endif
 
 namespace vvb {
 
@@ -90,14 +86,7 @@ extern "C" int vvbk_swiglu(const void* gate, const void* up, void* out, size_t n
     if (aligned16(gate) && aligned16(up) && aligned16(out)) {
         const size_t nvec = n / 8;
         const int tail = (int)(n - nvec * 8);
-        int unroll = kSwigluUnroll;
-#ifdef VVB_TUNING
-        if (const char* e = getenv("VVB_TUNE_SWIGLU_UNROLL")) unroll = atoi(e);
-        if (const char* e = getenv("VVB_TUNE_SWIGLU_BULK")) {
-            if (atoi(e) != 0 && tail == 0) return vvbk_swiglu_bulk(gate, up, out, nvec, stream, atoi(e));
-        }
-#endif
-        const size_t per_cta = (size_t)kSwigluThreads * unroll;
+        const size_t per_cta = (size_t)kSwigluThreads * kSwigluUnroll;
         size_t blocks = (nvec + per_cta - 1) / per_cta;
         if (blocks == 0) blocks = 1;
         if (blocks > 0x7fffffffu) return (int)cudaErrorInvalidValue;
@@ -105,18 +94,6 @@ extern "C" int vvbk_swiglu(const void* gate, const void* up, void* out, size_t n
         const __half* tu = (const __half*)up + nvec * 8;
         __half* to = (__half*)out + nvec * 8;
         const dim3 grid((unsigned)blocks, 1);
-#ifdef VVB_TUNING
-        if (unroll == 1)
-            launch_pdl(swiglu_vec_kernel<1>, grid, dim3(kSwigluThreads), 0, s, 
-                (const vec16*)gate, (const vec16*)up, (vec16*)out, nvec, 0, 0, 0, tg, tu, to, tail);
-        else if (unroll == 2)
-            launch_pdl(swiglu_vec_kernel<2>, grid, dim3(kSwigluThreads), 0, s, 
-                (const vec16*)gate, (const vec16*)up, (vec16*)out, nvec, 0, 0, 0, tg, tu, to, tail);
-        else if (unroll == 8)
-            launch_pdl(swiglu_vec_kernel<8>, grid, dim3(kSwigluThreads), 0, s, 
-                (const vec16*)gate, (const vec16*)up, (vec16*)out, nvec, 0, 0, 0, tg, tu, to, tail);
-        else
-#endif
         launch_pdl(swiglu_vec_kernel<kSwigluUnroll>, grid, dim3(kSwigluThreads), 0, s,
                    (const vec16*)gate, (const vec16*)up, (vec16*)out, nvec, 0, 0, 0, tg, tu, to, tail);
         g_launches.fetch_add(1, std::memory_order_relaxed);

@@ -3,8 +3,9 @@
  * 128-bit streaming loads/stores, FP16 pack/unpack, warp reductions.
  *
  * Everything on this path is read once and written once, so loads and stores
- * carry the streaming (evict-first) cache operator; the only reused data
- * (gamma, cos/sin) is staged in shared memory by the kernels themselves.
+ * carry the streaming (evict-first) cache operator; the only reused data are
+ * gamma (read through the read-only path, it stays in L1/L2) and the cos/sin
+ * values, which each RoPE CTA computes once into shared memory.
  */
 #pragma once
 #include <cuda_fp16.h>
@@ -128,13 +129,5 @@ static inline cudaError_t launch_pdl(void (*kernel)(P...), dim3 grid, dim3 block
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
 }
 #endif
-
-/* 16-byte asynchronous copy global -> shared (LDGSTS), L2-only caching. */
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
-    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem_src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
 
 }  // namespace vvb

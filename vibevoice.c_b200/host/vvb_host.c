@@ -15,10 +15,17 @@
  * one stream, run the three kernels on a second, and travel back on a third;
  * three sets of device buffers rotate so that slice i+1 uploads and slice i-1
  * downloads while slice i computes. The math runs only on the GPU.
+ *
+ * vvb_host_multi_t puts one such pipeline on each of several GPUs: a call
+ * splits the rows with vvb_shard_rows and drives every device from a host
+ * thread of its own (the reference's multi-device code also walks its devices
+ * from the host, src/inference/pipeline.c:389-513, src/cuda/cuda_utils.cu:301-325),
+ * so a caller with host buffers gets all the GPUs of the box from one call.
  */
 #include "vvb200.h"
 
 #include <cuda_runtime_api.h>
+#include <pthread.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -150,6 +157,11 @@ fail:
 
 vv_status_t vvb_layer_chain_host(vvb_host_ctx_t* c, const vvb_layer_chain_t* h) {
     if (!c || !h) return VV_ERR_NULL_PTR;
+    if (h->rows == 0) {                 /* nothing to do, whatever the pointers are */
+        c->last_h2d = c->last_d2h = 0;
+        c->last_ms = 0.0f;
+        return VV_OK;
+    }
     if (!h->hidden || !h->delta || !h->norm_w || !h->normed) return VV_ERR_NULL_PTR;
     if ((h->n_q_heads > 0 && !h->q) || (h->n_kv_heads > 0 && !h->k)) return VV_ERR_NULL_PTR;
     if (h->inter > 0 && (!h->gate || !h->up)) return VV_ERR_NULL_PTR;
@@ -212,7 +224,7 @@ vv_status_t vvb_layer_chain_host(vvb_host_ctx_t* c, const vvb_layer_chain_t* h) 
         CK(cudaEventRecord(s->downloaded, c->s_down));
         c->last_d2h += (uint64_t)n * (2 * hrow + qrow + krow + irow);
     }
-    /* the end marker waits for the last upload too (rows == 0: only gamma) */
+    /* the end marker waits for the last upload too */
     CK(cudaEventRecord(c->slot[0].uploaded, c->s_up));
     CK(cudaStreamWaitEvent(c->s_down, c->slot[0].uploaded, 0));
     CK(cudaEventRecord(c->t_end, c->s_down));
@@ -235,4 +247,117 @@ float vvb_host_ctx_last_ms(const vvb_host_ctx_t* c) { return c ? c->last_ms : 0.
 void vvb_host_ctx_last_traffic(const vvb_host_ctx_t* c, uint64_t* h2d_bytes, uint64_t* d2h_bytes) {
     if (h2d_bytes) *h2d_bytes = c ? c->last_h2d : 0;
     if (d2h_bytes) *d2h_bytes = c ? c->last_d2h : 0;
+}
+
+/* ----------------------------------------------------- several devices at once */
+
+struct vvb_host_multi {
+    int n;
+    vvb_host_ctx_t** ctx;      /* one pipeline per device */
+    float last_ms;
+    uint64_t last_h2d, last_d2h;
+};
+
+typedef struct vvb_multi_job {
+    vvb_host_ctx_t* ctx;
+    vvb_layer_chain_t shard;
+    vv_status_t status;
+} vvb_multi_job_t;
+
+static void* vvb_multi_worker(void* arg) {
+    vvb_multi_job_t* j = (vvb_multi_job_t*)arg;
+    j->status = vvb_layer_chain_host(j->ctx, &j->shard);   /* sets the device for this thread */
+    return NULL;
+}
+
+void vvb_host_multi_destroy(vvb_host_multi_t* m) {
+    if (!m) return;
+    if (m->ctx) {
+        for (int i = 0; i < m->n; i++) vvb_host_ctx_destroy(m->ctx[i]);
+        free(m->ctx);
+    }
+    free(m);
+}
+
+vv_status_t vvb_host_multi_create(vvb_host_multi_t** out, const int* devices, int n_devices,
+                                  int max_slice_rows, int hidden_size, int n_q_heads,
+                                  int n_kv_heads, int head_dim, int inter) {
+    if (!out) return VV_ERR_NULL_PTR;
+    *out = NULL;
+    if (n_devices <= 0 || n_devices > 64) return VV_ERR_INVALID_ARG;
+    vvb_host_multi_t* m = (vvb_host_multi_t*)calloc(1, sizeof *m);
+    if (!m) return VV_ERR_OUT_OF_MEMORY;
+    m->ctx = (vvb_host_ctx_t**)calloc((size_t)n_devices, sizeof *m->ctx);
+    if (!m->ctx) { free(m); return VV_ERR_OUT_OF_MEMORY; }
+    m->n = n_devices;
+    for (int i = 0; i < n_devices; i++) {
+        const int dev = devices ? devices[i] : i;      /* NULL: devices 0 .. n-1 */
+        const vv_status_t st = vvb_host_ctx_create(&m->ctx[i], dev, max_slice_rows, hidden_size,
+                                                   n_q_heads, n_kv_heads, head_dim, inter);
+        if (st != VV_OK) { vvb_host_multi_destroy(m); return st; }
+    }
+    *out = m;
+    return VV_OK;
+}
+
+int vvb_host_multi_devices(const vvb_host_multi_t* m) { return m ? m->n : 0; }
+
+vv_status_t vvb_layer_chain_host_multi(vvb_host_multi_t* m, const vvb_layer_chain_t* h) {
+    if (!m || !h) return VV_ERR_NULL_PTR;
+    if (h->rows < 0) return VV_ERR_INVALID_ARG;
+    if (m->n > 64) return VV_ERR_INVALID_ARG;
+    vvb_multi_job_t job[64];
+    pthread_t thread[64];
+    int started[64];
+    const size_t hrow = (size_t)h->hidden_size * 2u;
+    const size_t qrow = (size_t)h->n_q_heads * (size_t)h->head_dim * 2u;
+    const size_t krow = (size_t)h->n_kv_heads * (size_t)h->head_dim * 2u;
+    const size_t irow = (size_t)h->inter * 2u;
+    for (int g = 0; g < m->n; g++) {
+        int64_t first = 0, count = 0;
+        vv_status_t st = vvb_shard_rows(h->rows, m->n, g, &first, &count);
+        if (st != VV_OK) return st;
+        vvb_layer_chain_t* s = &job[g].shard;
+        *s = *h;
+        const size_t off = (size_t)first;
+        s->hidden = h->hidden ? (char*)h->hidden + off * hrow : NULL;
+        s->delta = h->delta ? (const char*)h->delta + off * hrow : NULL;
+        s->normed = h->normed ? (char*)h->normed + off * hrow : NULL;
+        s->q = h->q ? (char*)h->q + off * qrow : NULL;
+        s->k = h->k ? (char*)h->k + off * krow : NULL;
+        s->gate = h->gate ? (char*)h->gate + off * irow : NULL;
+        s->up = h->up ? (const char*)h->up + off * irow : NULL;
+        s->rows = (int)count;
+        s->position_offset = h->position_offset + (int)first;    /* the shard's first token position */
+        job[g].ctx = m->ctx[g];
+        job[g].status = VV_OK;
+    }
+    /* one host thread per device; the calling thread takes device 0's shard itself */
+    for (int g = 1; g < m->n; g++) {
+        started[g] = pthread_create(&thread[g], NULL, vvb_multi_worker, &job[g]) == 0;
+        if (!started[g]) vvb_multi_worker(&job[g]);      /* no thread to be had: run it here, in turn */
+    }
+    vvb_multi_worker(&job[0]);
+    for (int g = 1; g < m->n; g++)
+        if (started[g]) pthread_join(thread[g], NULL);
+    vv_status_t result = VV_OK;
+    m->last_ms = 0.0f;
+    m->last_h2d = m->last_d2h = 0;
+    for (int g = 0; g < m->n; g++) {
+        if (job[g].status != VV_OK && result == VV_OK) result = job[g].status;
+        const float ms = vvb_host_ctx_last_ms(m->ctx[g]);
+        if (ms > m->last_ms) m->last_ms = ms;
+        uint64_t a = 0, b = 0;
+        vvb_host_ctx_last_traffic(m->ctx[g], &a, &b);
+        m->last_h2d += a;
+        m->last_d2h += b;
+    }
+    return result;
+}
+
+float vvb_host_multi_last_ms(const vvb_host_multi_t* m) { return m ? m->last_ms : 0.0f; }
+
+void vvb_host_multi_last_traffic(const vvb_host_multi_t* m, uint64_t* h2d_bytes, uint64_t* d2h_bytes) {
+    if (h2d_bytes) *h2d_bytes = m ? m->last_h2d : 0;
+    if (d2h_bytes) *d2h_bytes = m ? m->last_d2h : 0;
 }

@@ -219,6 +219,7 @@ vv_status_t vvb_layer_chain_dev(const vvb_layer_chain_t* c, void* stream) {
     if (c->rows < 0 || c->hidden_size < 0 || c->inter < 0 || c->n_q_heads < 0 ||
         c->n_kv_heads < 0 || c->head_dim < 0)
         return VV_ERR_INVALID_ARG;
+    if (c->rows == 0) return VV_OK;      /* nothing to do, whatever the pointers are */
     /* The three operations touch disjoint tensors: when the shapes allow it
      * they go out as one grid (csrc/chain.cu), else as three launches. */
     if (c->rows > 0 && c->hidden && c->delta && c->norm_w && c->normed && c->q && c->k &&

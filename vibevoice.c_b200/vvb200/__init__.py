@@ -106,6 +106,12 @@ SIGNATURES = {
     "vvb_layer_chain_host": (_i, [_vp, C.POINTER(LayerChain)]),
     "vvb_host_ctx_last_traffic": (None, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "vvb_host_ctx_last_ms": (C.c_float, [_vp]),
+    "vvb_host_multi_create": (_i, [C.POINTER(_vp), C.POINTER(_i), _i, _i, _i, _i, _i, _i, _i]),
+    "vvb_host_multi_destroy": (None, [_vp]),
+    "vvb_host_multi_devices": (_i, [_vp]),
+    "vvb_layer_chain_host_multi": (_i, [_vp, C.POINTER(LayerChain)]),
+    "vvb_host_multi_last_ms": (C.c_float, [_vp]),
+    "vvb_host_multi_last_traffic": (None, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "vvb_version": (C.c_char_p, []),
     "vvb_status_string": (C.c_char_p, [_i]),
     "vvb_launch_count": (C.c_uint64, []),
@@ -347,6 +353,43 @@ class HostPipeline:
     def close(self):
         if self._ctx:
             _lib.vvb_host_ctx_destroy(self._ctx)
+            self._ctx = _vp()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class HostPipelineMulti:
+    """vvb_host_multi_t: HostPipeline on several GPUs of one box, one host thread
+    per device inside the library; rows are sharded with vvb_shard_rows."""
+
+    def __init__(self, devices, max_slice_rows, hidden_size, n_q_heads, n_kv_heads, head_dim, inter):
+        devices = list(devices)
+        arr = (_i * len(devices))(*devices)
+        self._ctx = _vp()
+        check(_lib.vvb_host_multi_create(C.byref(self._ctx), arr, len(devices), max_slice_rows, hidden_size,
+                                         n_q_heads, n_kv_heads, head_dim, inter), "vvb_host_multi_create")
+
+    def run(self, chain: LayerChain) -> int:
+        return _lib.vvb_layer_chain_host_multi(self._ctx, C.byref(chain))
+
+    def devices(self) -> int:
+        return int(_lib.vvb_host_multi_devices(self._ctx))
+
+    def last_traffic(self):
+        a, b = C.c_uint64(), C.c_uint64()
+        _lib.vvb_host_multi_last_traffic(self._ctx, C.byref(a), C.byref(b))
+        return a.value, b.value
+
+    def last_ms(self) -> float:
+        return float(_lib.vvb_host_multi_last_ms(self._ctx))
+
+    def close(self):
+        if self._ctx:
+            _lib.vvb_host_multi_destroy(self._ctx)
             self._ctx = _vp()
 
     def __del__(self):
