@@ -93,8 +93,9 @@ class Runner:
         self.clock = _Clock()
         self.out = []
 
-    def wanted(self, name):
-        return self.only is None or self.only in name
+    def wanted(self, *names):
+        """True when the --case filter selects any of these case names."""
+        return self.only is None or any(self.only in n for n in names)
 
     def case(self, name, config, make_set, call, set_bytes, algo_bytes, iters=40):
         if not self.wanted(name):
@@ -133,6 +134,29 @@ def run(peak_gbs: float, peak_kind: str, only=None, plain=False):
     w = (1 + 0.02 * torch.randn(H, device=dev)).half()
     R = Runner(peak_gbs, peak_kind, only, plain)
 
+    u8 = lambda *s: torch.empty(*s, device=dev, dtype=torch.uint8)
+    # First, while the GPU is still at its idle clock (the long streams below pull a 1 kW part
+    # into its power cap and the one-token sequence is launch-latency bound, so it feels the clock):
+    # the decode tail: final RMSNorm + LM head [152064, 3584] + argmax (two launches), and the plain GEMV
+    V = 152064
+    need_head = R.wanted("final_norm + lm_head + argmax [152064,3584]", "lm_head_gemv [152064,3584] (logits)",
+                         "decode step, 28 layers, M=1 (row kernels + LM head only)")
+    if need_head:
+        head = torch.empty(V, H, device=dev, dtype=torch.float16).normal_(0, 0.02)
+        sbytes = vv.vvb_lm_head_scratch_bytes(V)
+        mk = lambda: (rn(H), u8(sbytes), torch.empty(1, device=dev, dtype=torch.int32),
+                      torch.empty(V, device=dev, dtype=torch.float32))
+        if not plain and R.wanted("decode step, 28 layers, M=1 (row kernels + LM head only)"):
+            R.out.append(decode_step(dev, head, w, R.clock))
+        R.case("final_norm + lm_head + argmax [152064,3584]", None, mk,
+               lambda b, s: _ok(vv.vvb_lm_head_argmax_dev(b[0], w, 1e-6, head, V, H, None, b[1], sbytes, b[2], None, s)),
+               V * H * 2, V * H * 2 + 2 * H * 2, iters=10)
+        R.case("lm_head_gemv [152064,3584] (logits)", None, mk,
+               lambda b, s: _ok(vv.vv_lm_head_gemv_dev(b[0], head, b[3], V, H, s)),
+               V * H * 2, V * H * 2 + V * 4, iters=10)
+        del head
+        torch.cuda.empty_cache()
+
     # config 1 (and the same op at prefill sizes): residual add + RMSNorm
     for rows, cfg in ((512, 1), (4096, None), (T, 5)):
         R.case(f"add_rmsnorm [{rows},3584]", cfg, lambda: (rn(rows, H), rn(rows, H), f16(rows, H)),
@@ -150,7 +174,7 @@ def run(peak_gbs: float, peak_kind: str, only=None, plain=False):
                rows * INTER * 2 * 2, rows * INTER * 2 * 3, iters=20 if rows > 4096 else 40)
     # config 4: gather 16384 rows of [151936, 3584] + RMSNorm (fused), and the plain gather
     rows = 16384
-    if R.wanted("embedding"):
+    if R.wanted("embedding_rmsnorm 16384 of [151936,3584]", "embedding 16384 of [151936,3584]"):
         table = torch.empty(VOCAB, H, device=dev, dtype=torch.float16).normal_(0, 0.02)
         mk_ids = lambda: torch.randint(0, VOCAB, (rows,), device=dev, dtype=torch.int32)
         R.case("embedding_rmsnorm 16384 of [151936,3584]", 4, lambda: (mk_ids(), f16(rows, H), f16(rows, H)),
@@ -170,6 +194,17 @@ def run(peak_gbs: float, peak_kind: str, only=None, plain=False):
     R.case("bias_add [14449,3584]", None, lambda: (rn(rows, NQ * HD),),
            lambda b, s: _ok(vv.vv_bias_add_dev(b[0], bias, rows, NQ * HD, s)),
            rows * H * 2, rows * H * 4 + 2 * H)
+    f32 = lambda *s: torch.empty(*s, device=dev, dtype=torch.float32)
+    R.case("fp32_to_fp16 [14449,3584]", None, lambda: (torch.randn(rows, H, device=dev), f16(rows, H)),
+           lambda b, s: _ok(vv.vv_fp32_to_fp16_dev(b[0], b[1], rows * H, s)),
+           rows * H * 6, rows * H * 6)
+    R.case("fp16_to_fp32 [14449,3584]", None, lambda: (rn(rows, H), f32(rows, H)),
+           lambda b, s: _ok(vv.vv_fp16_to_fp32_dev(b[0], b[1], rows * H, s)),
+           rows * H * 6, rows * H * 6)
+    # the plain norm (no addend), as it runs over rows the gather wrote
+    R.case("rmsnorm [14449,3584]", None, lambda: (rn(rows, H), f16(rows, H)),
+           lambda b, s: _ok(vv.vv_rmsnorm_dev(b[0], w, b[1], rows, H, 1e-6, s)),
+           rows * H * 4, rows * H * 4 + 2 * H)
     # bias + RoPE + KV-cache append in one launch (Q in place; K, V read once and written into the cache)
     bq, bk, bv = rn(NQ * HD), rn(NKV * HD), rn(NKV * HD)
     R.case("rope_qk_append [14449,28+4+4,128] with biases", None,
@@ -179,7 +214,6 @@ def run(peak_gbs: float, peak_kind: str, only=None, plain=False):
            rows * (NQ + 4 * NKV) * HD * 2, rows * (2 * NQ + 4 * NKV) * HD * 2)
     # the same launch for the FP8 (E4M3) KV cache: K and V leave as one byte per element, K minus a reference key
     kref = rn(NKV * HD)
-    u8 = lambda *s: torch.empty(*s, device=dev, dtype=torch.uint8)
     R.case("rope_qk_append_fp8 [14449,28+4+4,128] with biases, e4m3 cache, reference key", None,
            lambda: (rn(rows, NQ, HD), rn(rows, NKV, HD), rn(rows, NKV, HD), u8(rows, NKV * HD), u8(rows, NKV * HD)),
            lambda b, s: _ok(vv.vvb_rope_qk_append_fp8_dev(b[0], b[1], b[2], bq, bk, bv, b[3], b[4], kref, rows, NQ, NKV,
@@ -204,24 +238,6 @@ def run(peak_gbs: float, peak_kind: str, only=None, plain=False):
            lambda b, s: _ok(vv.vv_act_quant_dev(b[0], rows, H, 0, b[1], b[2], b[3], s)),
            rows * H * 2 + qout(H), rows * H * 2 + qout(H))
 
-    # the decode tail: final RMSNorm + LM head [152064, 3584] + argmax (two launches), and the plain GEMV
-    V = 152064
-    need_head = R.wanted("lm_head") or R.wanted("decode step")
-    if need_head:
-        head = torch.empty(V, H, device=dev, dtype=torch.float16).normal_(0, 0.02)
-        sbytes = vv.vvb_lm_head_scratch_bytes(V)
-        mk = lambda: (rn(H), u8(sbytes), torch.empty(1, device=dev, dtype=torch.int32),
-                      torch.empty(V, device=dev, dtype=torch.float32))
-        R.case("final_norm + lm_head + argmax [152064,3584]", None, mk,
-               lambda b, s: _ok(vv.vvb_lm_head_argmax_dev(b[0], w, 1e-6, head, V, H, None, b[1], sbytes, b[2], None, s)),
-               V * H * 2, V * H * 2 + 2 * H * 2, iters=10)
-        R.case("lm_head_gemv [152064,3584] (logits)", None, mk,
-               lambda b, s: _ok(vv.vv_lm_head_gemv_dev(b[0], head, b[3], V, H, s)),
-               V * H * 2, V * H * 2 + V * 4, iters=10)
-        if not plain and R.wanted("decode step"):
-            R.out.append(decode_step(dev, head, w, R.clock))
-        del head
-        torch.cuda.empty_cache()
     return {"workload": "kernels", "peak_GB/s": peak_gbs, "peak_kind": "of " + peak_kind,
             "nominal_GB/s": NOMINAL_HBM_GBS,
             "method": "each op alone: CUDA-graph replay of back-to-back launches over rotating buffer sets > 2.5x L2, "

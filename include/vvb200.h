@@ -236,6 +236,10 @@ vv_status_t vvb_rope_qk_append_dev(void* q, void* k, const void* v,
 #define VVB_KV_FP16     0
 #define VVB_KV_FP8_E4M3 1
 #define VVB_KV_FP8_E5M2 2
+#define VVB_KV_TQ4      3   /* TurboQuant 4 / 3 / 2 / 1.5 bits per value: include/vibevoice/kv_quant.h:37-40 */
+#define VVB_KV_TQ3      4
+#define VVB_KV_TQ2      5
+#define VVB_KV_TQ1_5    6
 
 /** vvb_rope_qk_append_dev for the FP8 KV cache: the same single launch, but the
  *  cache rows receive the reference's software FP8 byte of every value (one
@@ -266,7 +270,17 @@ vv_status_t vvb_rope_qk_append_fp8_dev(void* q, void* k, const void* v,
  *  vv_kv_store_dev applies (src/cuda/kv_quant.cu:508-551). page_table is a
  *  device array with an entry for every page the call touches; NULL means a
  *  contiguous cache (row t). kv_format: VVB_KV_FP16 (k_ref ignored),
- *  VVB_KV_FP8_E4M3 or VVB_KV_FP8_E5M2. Everything else as documented for
+ *  VVB_KV_FP8_E4M3 or VVB_KV_FP8_E5M2, or one of the four TurboQuant formats
+ *  VVB_KV_TQ4 / TQ3 / TQ2 / TQ1_5 (head_dim 128 only, as in the reference). For
+ *  those, each 128-wide head vector -- K after bias, rotation, rounding to FP16
+ *  and minus k_ref; V after its bias -- is stored as the reference's
+ *  vv_kv_quant_store_dev stores it (src/cuda/kv_quant.cu:85-120): randomized
+ *  Hadamard transform, quantization against the vector's RMS with the format's
+ *  Lloyd-Max code book, head_dim * bits / 8 bytes of codes in k_store / v_store
+ *  ([max_len, n_kv_heads * bytes_per_vec]) and the RMS as FP16 in k_meta /
+ *  v_meta ([max_len, n_kv_heads], required). The bytes are those of the
+ *  reference's kernel (same operations in the same order, its fast-math square
+ *  root and reciprocal included). Everything else as documented for
  *  vvb_rope_qk_append_dev and vvb_rope_qk_append_fp8_dev, which are this call
  *  with page_table == NULL. */
 typedef struct vvb_kv_append {
@@ -276,9 +290,9 @@ typedef struct vvb_kv_append {
     const void* q_bias;        /* [n_q_heads * head_dim] or NULL                           */
     const void* k_bias;        /* [n_kv_heads * head_dim] or NULL                          */
     const void* v_bias;        /* [n_kv_heads * head_dim] or NULL                          */
-    void* k_store;             /* one layer's K cache rows: FP16 or one byte per element   */
+    void* k_store;             /* one layer's K cache rows: FP16, bytes, or packed codes   */
     void* v_store;             /* one layer's V cache rows                                 */
-    const void* k_ref;         /* FP8 only: FP16 [n_kv_heads * head_dim] or NULL           */
+    const void* k_ref;         /* FP8 / TurboQuant: FP16 [n_kv_heads * head_dim] or NULL   */
     const int* page_table;     /* device ints or NULL                                      */
     const int* d_position;     /* device int or NULL                                       */
     int rows, n_q_heads, n_kv_heads, head_dim;
@@ -287,6 +301,8 @@ typedef struct vvb_kv_append {
     float theta;
     int kv_format;
     int keep_k;
+    void* k_meta;              /* TurboQuant only: FP16 [max_len, n_kv_heads], else NULL   */
+    void* v_meta;
 } vvb_kv_append_t;
 
 vv_status_t vvb_kv_append_dev(const vvb_kv_append_t* args, void* stream);

@@ -163,6 +163,51 @@ class _Restated:
         assert st == 0, st
         return out
 
+    # --- TurboQuant KV formats (fmt 3..6 = 4, 3, 2, 1.5 bits per value) --------
+    def tq_bytes_per_vec(self, fmt):
+        self.lib.orc_tq_bytes_per_vec.argtypes = [C.c_int]
+        return int(self.lib.orc_tq_bytes_per_vec(int(fmt)))
+
+    def tq_rotate(self, x_f32):
+        """Sign flips + 128-point Walsh-Hadamard transform + 1/sqrt(128), on the last axis (128)."""
+        self.lib.orc_tq_rotate128.argtypes = [_f32p]
+        out = np.ascontiguousarray(x_f32, dtype=np.float32).copy()
+        flat = out.reshape(-1, 128)
+        for r in flat:
+            self.lib.orc_tq_rotate128(r.ctypes.data_as(_f32p))
+        return out
+
+    def kv_store_tq(self, x_f16, ref_f16, fmt, first_row=0, store=None, meta=None):
+        """FP16 [n_pos, n_heads, 128] (minus ref [n_heads, 128], in float) -> (codes uint8
+        [first_row + n_pos, n_heads * bytes_per_vec], sigma float16 [first_row + n_pos, n_heads]);
+        rows first_row.. are written into `store` / `meta` when given."""
+        L = self.lib
+        L.orc_kv_store_tq.argtypes = [_u16p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        x = _as_u16(np.ascontiguousarray(x_f16))
+        n_pos, n_heads, hd = x.shape
+        assert hd == 128
+        bpv = self.tq_bytes_per_vec(fmt)
+        if store is None:
+            store = np.zeros((first_row + n_pos, n_heads * bpv), np.uint8)
+        if meta is None:
+            meta = np.zeros((first_row + n_pos, n_heads), np.float16)
+        r = _as_u16(np.ascontiguousarray(ref_f16)) if ref_f16 is not None else None
+        st = L.orc_kv_store_tq(_ptr(x, _u16p), r.ctypes.data if r is not None else None, n_pos, n_heads,
+                               int(first_row), int(fmt), store.ctypes.data, meta.ctypes.data)
+        assert st == 0, st
+        return store, meta
+
+    def kv_load_tq(self, vec_bytes, sigma_f16, fmt):
+        """One stored vector back to its 128 ROTATED-domain values (sigma * level[code])."""
+        L = self.lib
+        L.orc_kv_load_tq.argtypes = [C.c_void_p, C.c_uint16, C.c_int, _f32p]
+        vec = np.ascontiguousarray(vec_bytes, dtype=np.uint8)
+        out = np.empty(128, np.float32)
+        sig = int(np.array([sigma_f16], np.float16).view(np.uint16)[0])
+        st = L.orc_kv_load_tq(vec.ctypes.data, sig, int(fmt), _ptr(out, _f32p))
+        assert st == 0, st
+        return out
+
     def quant_act_q8(self, x_f32, layout, want_xsum=True):
         """Per-token int8 quantizer on FP32 rows [M, K]: (xq int8 [M,K],
         sx float32 [M], xsum int32 [M, K/32] or None)."""

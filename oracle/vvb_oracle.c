@@ -427,3 +427,164 @@ float orc_fp8_decode(uint8_t v, int fmt) {
     const float r = (e == 0) ? ldexpf((float)m, 1 - bias - M) : ldexpf(1.0f + (float)m / (float)(1 << M), e - bias);
     return (v & 0x80) ? -r : r;
 }
+
+/* ---- TurboQuant KV-cache formats (include/vibevoice/kv_quant.h:37-40) ---------
+ * The store of src/cuda/kv_quant.cu:40-121 for formats 3..6 (4, 3, 2 and 1.5
+ * bits per value), one 128-wide head vector at a time:
+ *   v = half -> float, minus the layer's reference key in float (:60-73);
+ *   v[d] *= sign(d), a fixed +-1 pattern hashed from the index
+ *     (src/cuda/kv_codec.cuh:133-137);
+ *   a 128-point Walsh-Hadamard transform, seven butterfly stages of stride
+ *     1, 2, 4 .. 64 (kv_codec.cuh:145-163: two stages inside a lane's four
+ *     values, five across lanes; each stage is lower + upper / lower - upper
+ *     on the previous stage's values), then v *= 1/sqrt(128) as a float
+ *     constant (kv_codec.cuh:64);
+ *   sigma = sqrtf(max(sum(v*v) / 128, 1e-12)), the sum taken as the device takes
+ *     it: a fused multiply-add chain over each lane's four values, then a
+ *     butterfly of pairwise float additions across the 32 lanes (:92-95);
+ *   each value is coded by the number of decision thresholds 0.5 * (level[j] +
+ *     level[j + 1]) that v / sigma exceeds (kv_codec.cuh:232-266); the 1.5-bit
+ *     format codes PAIRS of values by the nearest of eight 2-D code words
+ *     (:267-288);
+ *   lane L's codes occupy bits [nb * L, nb * (L + 1)) of the vector's bytes,
+ *     little endian (:99-117), and sigma is kept as FP16 beside them (:118-119).
+ * The device kernel is compiled with fast-math: its square root and reciprocal
+ * are the hardware approximations and it flushes subnormals, where this file
+ * uses sqrtf and a division. The two agree except when v / sigma lands within
+ * a few float ulps of a threshold, or sigma within as much of a FP16 rounding
+ * boundary; tests compare with that allowance. The code books are the
+ * format's definition (Lloyd-Max levels of a unit Gaussian, kv_codec.cuh:42-62)
+ * and are restated here digit for digit: a reader needs the same numbers. */
+static const float orc_lev4[16] = {-2.725112f, -2.065280f, -1.613787f, -1.251845f, -0.938657f, -0.654379f,
+                                   -0.386970f, -0.127960f, +0.127960f, +0.386970f, +0.654379f, +0.938657f,
+                                   +1.251845f, +1.613787f, +2.065280f, +2.725112f};
+static const float orc_lev3[8] = {-2.150300f, -1.343258f, -0.755588f, -0.244756f,
+                                  +0.244756f, +0.755588f, +1.343258f, +2.150300f};
+static const float orc_lev2[4] = {-1.511418f, -0.452456f, +0.452456f, +1.511418f};
+static const float orc_vq15[16] = {-1.500251f, +0.674678f, -1.127883f, -0.787015f, -0.283251f, +0.390133f,
+                                   -0.103102f, +1.624620f, +0.100120f, -1.618563f, +0.286482f, -0.379555f,
+                                   +1.134227f, +0.790368f, +1.496572f, -0.666578f};
+#define ORC_WHT_NORM 0.0883883476f
+
+float orc_kv_sign(int d) {
+    uint32_t h = (uint32_t)d * 2654435761u + 0x9E3779B9u;
+    h ^= h >> 15;
+    h *= 0x85EBCA6Bu;
+    h ^= h >> 13;
+    return (h & 1u) ? -1.0f : 1.0f;
+}
+
+/* fmt 3..6 -> bits per lane of four values (kv_codec.cuh:181-185). */
+static int orc_tq_lane_bits(int fmt) { return fmt == 3 ? 16 : fmt == 4 ? 12 : fmt == 5 ? 8 : fmt == 6 ? 6 : 0; }
+int orc_tq_bytes_per_vec(int fmt) { return orc_tq_lane_bits(fmt) * 4; }     /* 32 lanes * bits / 8 */
+
+/* The rotation alone (sign flips, transform, scale): what vv_kv_rotate_dev
+ * applies to Q (src/cuda/kv_quant.cu:175-205, forward direction). In place. */
+void orc_tq_rotate128(float v[128]) {
+    for (int d = 0; d < 128; d++) v[d] *= orc_kv_sign(d);
+    for (int s = 1; s < 128; s <<= 1)
+        for (int d = 0; d < 128; d++)
+            if (!(d & s)) {
+                const float lo = v[d], hi = v[d + s];
+                v[d] = lo + hi;
+                v[d + s] = lo - hi;
+            }
+    for (int d = 0; d < 128; d++) v[d] *= ORC_WHT_NORM;
+}
+
+static uint32_t orc_tq_pack4(const float y[4], float inv_sigma, int fmt) {
+    uint32_t bits = 0;
+    if (fmt == 6) {
+        for (int p = 0; p < 2; p++) {
+            const float a = y[2 * p] * inv_sigma, b = y[2 * p + 1] * inv_sigma;
+            uint32_t best = 0;
+            float bd = 3.402823466e+38f;
+            for (uint32_t c = 0; c < 8; c++) {
+                const float da = a - orc_vq15[2 * c], db = b - orc_vq15[2 * c + 1];
+                const float d = fmaf(da, da, db * db);      /* the device contracts da*da + db*db */
+                if (d < bd) { bd = d; best = c; }
+            }
+            bits |= best << (3 * p);
+        }
+        return bits;
+    }
+    const float* lev = fmt == 3 ? orc_lev4 : fmt == 4 ? orc_lev3 : orc_lev2;
+    const int nlev = fmt == 3 ? 16 : fmt == 4 ? 8 : 4;
+    const int w = fmt == 3 ? 4 : fmt == 4 ? 3 : 2;
+    for (int i = 0; i < 4; i++) {
+        const float t = y[i] * inv_sigma;
+        uint32_t c = 0;
+        for (int j = 0; j + 1 < nlev; j++) c += (t > 0.5f * (lev[j] + lev[j + 1])) ? 1u : 0u;
+        bits |= c << (w * i);
+    }
+    return bits;
+}
+
+/* x: FP16 [n_pos, n_heads, 128]; ref (may be null): FP16 [n_heads, 128];
+ * store: bytes [first_row + n_pos, n_heads, bytes_per_vec]; meta: FP16
+ * [first_row + n_pos, n_heads]; rows first_row.. are written. */
+int orc_kv_store_tq(const uint16_t* x_f16, const uint16_t* ref_f16, int n_pos, int n_heads, int first_row, int fmt,
+                    uint8_t* store, uint16_t* meta) {
+    if (!x_f16 || !store || !meta) return ORC_ERR_NULL_PTR;
+    const int nb = orc_tq_lane_bits(fmt);
+    if (n_pos < 0 || n_heads <= 0 || first_row < 0 || nb == 0) return ORC_ERR_INVALID_ARG;
+    const int bpv = nb * 4;
+    for (int p = 0; p < n_pos; p++) {
+        for (int h = 0; h < n_heads; h++) {
+            float v[128];
+            const uint16_t* src = x_f16 + ((size_t)p * n_heads + h) * 128;
+            for (int d = 0; d < 128; d++) {
+                v[d] = orc_half_to_float(src[d]);
+                if (ref_f16) v[d] -= orc_half_to_float(ref_f16[(size_t)h * 128 + d]);
+            }
+            orc_tq_rotate128(v);
+            float part[32];
+            for (int l = 0; l < 32; l++) {
+                float ss = 0.0f;
+                for (int i = 0; i < 4; i++) ss = fmaf(v[4 * l + i], v[4 * l + i], ss);
+                part[l] = ss;
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                float next[32];
+                for (int l = 0; l < 32; l++) next[l] = part[l] + part[l ^ o];
+                memcpy(part, next, sizeof part);
+            }
+            const float sigma = sqrtf(fmaxf(part[0] / 128.0f, 1e-12f));
+            const float inv_sigma = 1.0f / sigma;
+            uint32_t words[16] = {0};
+            for (int l = 0; l < 32; l++) {
+                const uint32_t bits = orc_tq_pack4(v + 4 * l, inv_sigma, fmt);
+                const int bit = nb * l;
+                words[bit >> 5] |= bits << (bit & 31);
+                if ((bit & 31) + nb > 32) words[(bit >> 5) + 1] |= bits >> (32 - (bit & 31));
+            }
+            const size_t row = (size_t)(first_row + p) * n_heads + h;
+            memcpy(store + row * (size_t)bpv, words, (size_t)bpv);      /* little-endian host, as the device */
+            meta[row] = orc_float_to_half_rne(sigma);
+        }
+    }
+    return ORC_OK;
+}
+
+/* Decoding one stored vector back to the ROTATED domain (kv_codec.cuh:207-229):
+ * value = sigma * level[code]. For round-trip checks. */
+int orc_kv_load_tq(const uint8_t* vec, uint16_t sigma_f16, int fmt, float out[128]) {
+    const int nb = orc_tq_lane_bits(fmt);
+    if (!vec || !out) return ORC_ERR_NULL_PTR;
+    if (nb == 0) return ORC_ERR_INVALID_ARG;
+    const float sigma = orc_half_to_float(sigma_f16);
+    uint32_t words[17] = {0};
+    memcpy(words, vec, (size_t)nb * 4);
+    for (int l = 0; l < 32; l++) {
+        const int bit = nb * l, wi = bit >> 5, sh = bit & 31;
+        uint32_t b = sh ? ((words[wi] >> sh) | (words[wi + 1] << (32 - sh))) : words[wi];
+        b &= (1u << nb) - 1u;
+        for (int i = 0; i < 4; i++) {
+            if (fmt == 3) out[4 * l + i] = sigma * orc_lev4[(b >> (4 * i)) & 15u];
+            else if (fmt == 4) out[4 * l + i] = sigma * orc_lev3[(b >> (3 * i)) & 7u];
+            else if (fmt == 5) out[4 * l + i] = sigma * orc_lev2[(b >> (2 * i)) & 3u];
+            else out[4 * l + i] = sigma * orc_vq15[2 * ((b >> (3 * (i >> 1))) & 7u) + (i & 1)];
+        }
+    }
+    return ORC_OK;
+}

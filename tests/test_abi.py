@@ -139,7 +139,8 @@ def test_argument_validation_needs_no_gpu(vv):
                                            28, 4, 128, stream=0, **kw)
     assert kv(q=None) == vv.VV_ERR_NULL_PTR and kv(k=None) == vv.VV_ERR_NULL_PTR and kv(ks=None) == vv.VV_ERR_NULL_PTR
     assert kv(rows=-1) == vv.VV_ERR_INVALID_ARG and kv(cache_offset=-1) == vv.VV_ERR_INVALID_ARG
-    assert kv(kv_format=3) == vv.VV_ERR_UNSUPPORTED and kv(kv_format=-1) == vv.VV_ERR_UNSUPPORTED   # TurboQuant: not here
+    assert kv(kv_format=7) == vv.VV_ERR_UNSUPPORTED and kv(kv_format=-1) == vv.VV_ERR_UNSUPPORTED
+    assert kv(kv_format=3) == vv.VV_ERR_NULL_PTR          # TurboQuant needs the two sigma arrays
     assert kv(rows=0) == vv.VV_OK and kv(rows=0, kv_format=2, page_table=P) == vv.VV_OK
     assert vv.vvb_rope_qk_append_dev(P, P, None, None, None, None, P, P, 1, 28, 4, 128, 0, 0, None, 1e6, 0, 0) \
         == vv.VV_ERR_NULL_PTR

@@ -311,7 +311,7 @@ static void launch_q_vpt(const ActQuantArgs& a, int threads, cudaStream_t s) {
 
 template <int MODE>
 static cudaError_t launch_q(const ActQuantArgs& a, cudaStream_t s) {
-    if (MODE != Q_SWIGLU) {
+    if constexpr (MODE != Q_SWIGLU) {
         bool done = true;
         switch (two_warp_vpt(a.rows, a.nvec, MODE)) {
             case 3: launch_two_warp<3, MODE>(a, s); break;

@@ -26,28 +26,15 @@ namespace vvb {
 
 extern std::atomic<uint64_t> g_launches;
 
-#ifndef VVB_CHAIN_THREADS
-#define VVB_CHAIN_THREADS 256
-#endif
-constexpr int kChainThreads = VVB_CHAIN_THREADS;
+constexpr int kChainThreads = 256;
 constexpr int kChainNormGroup = 128;     /* threads per row */
 constexpr int kChainNormVPT = 4;         /* => hidden <= 128 * 4 * 8 = 4096 */
-/* Build-time shape choices (the defaults are the measured best):
- * VVB_CHAIN_SWIGLU_UNROLL  vectors of gate (and of up) per thread of a SwiGLU CTA;
- * VVB_CHAIN_ORDER          block-index order of the three kinds of CTA:
- *                          0 [norm | rope | swiglu], 1 [swiglu | norm | rope],
- *                          2 [swiglu | rope | norm]. */
+/* Vectors of gate (and of up) per thread of a SwiGLU CTA. Inside this kernel
+ * (three 256-thread CTAs per SM) four is the measured best: 324 us per step at
+ * 14449 rows and 45.1 us at 1807 against 360 / 49.1 with two and 448 / 59.4 with
+ * one, which leave too few bytes in flight per SM. */
 #ifndef VVB_CHAIN_SWIGLU_UNROLL
 #define VVB_CHAIN_SWIGLU_UNROLL 4
-#endif
-#ifndef VVB_CHAIN_ORDER
-#define VVB_CHAIN_ORDER 0
-#endif
-/* VVB_CHAIN_TAIL_UNROLL  0: off. Otherwise the last wave's worth of SwiGLU vectors goes out in
- *                        CTAs of this many vectors per thread (smaller than the bulk's), so that
- *                        the grid drains in shorter steps. Order 0 only. */
-#ifndef VVB_CHAIN_TAIL_UNROLL
-#define VVB_CHAIN_TAIL_UNROLL 0
 #endif
 constexpr int kChainSwigluUnroll = VVB_CHAIN_SWIGLU_UNROLL;
 
@@ -65,7 +52,7 @@ struct ChainArgs {
     const vec16* up;
     vec16* out;
     size_t swiglu_vecs;
-    unsigned norm_ctas, rope_gx, rope_ctas, swiglu_ctas, swiglu_bulk_ctas;
+    unsigned norm_ctas, rope_gx, rope_ctas;
 };
 
 template <int NORM_GUARD>
@@ -75,20 +62,6 @@ layer_chain_kernel(const __grid_constant__ ChainArgs a) {
     pdl_trigger();
     unsigned b = blockIdx.x;
     const int t = threadIdx.x;
-#if VVB_CHAIN_ORDER != 0
-    if (b < a.swiglu_ctas) {
-        swiglu_stream_body<kChainSwigluUnroll, kChainThreads>(a.gate, a.up, a.out, a.swiglu_vecs, b, t);
-        return;
-    }
-    b -= a.swiglu_ctas;
-#endif
-#if VVB_CHAIN_ORDER == 2
-    if (b < a.rope_ctas) {
-        rope_tile_body<kChainThreads>(a.rope, (int)(b % a.rope_gx), (int)(b / a.rope_gx));
-        return;
-    }
-    b -= a.rope_ctas;
-#endif
     if (b < a.norm_ctas) {
         const int grp = t / kChainNormGroup;
         row_norm_body<kChainNormVPT, kChainThreads / kChainNormGroup, NORM_GUARD>(
@@ -96,28 +69,13 @@ layer_chain_kernel(const __grid_constant__ ChainArgs a) {
             kChainNormGroup, grp);
         return;
     }
-#if VVB_CHAIN_ORDER != 2
     b -= a.norm_ctas;
     if (b < a.rope_ctas) {
-        rope_tile_body<kChainThreads>(a.rope, (int)(b % a.rope_gx), (int)(b / a.rope_gx));
+        rope_tile_body(a.rope, (int)(b % a.rope_gx), (int)(b / a.rope_gx));
         return;
     }
-#endif
-#if VVB_CHAIN_ORDER == 0
     b -= a.rope_ctas;
-#if VVB_CHAIN_TAIL_UNROLL > 0
-    if (b >= a.swiglu_bulk_ctas) {
-        const size_t done = (size_t)a.swiglu_bulk_ctas * (size_t)(kChainThreads * kChainSwigluUnroll);
-        swiglu_stream_body<VVB_CHAIN_TAIL_UNROLL, kChainThreads>(a.gate + done, a.up + done, a.out + done,
-                                                                 a.swiglu_vecs - done, b - a.swiglu_bulk_ctas, t);
-        return;
-    }
-    swiglu_stream_body<kChainSwigluUnroll, kChainThreads>(
-        a.gate, a.up, a.out, (size_t)a.swiglu_bulk_ctas * (size_t)(kChainThreads * kChainSwigluUnroll), b, t);
-#else
     swiglu_stream_body<kChainSwigluUnroll, kChainThreads>(a.gate, a.up, a.out, a.swiglu_vecs, b, t);
-#endif
-#endif
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -147,7 +105,7 @@ extern "C" int vvbk_layer_chain(void* hidden, const void* delta, const void* wei
     a.norm = make_row_norm_args(hidden, delta, nullptr, hidden, weight, normed, rows, hidden_size, 0, eps);
     unsigned gx, gy;
     rope_plan(a.rope, q, k, rows, n_q_heads, n_kv_heads, head_dim, position_offset, nullptr, inv_freq,
-              kRopeMaxRowsPerThread, &gx, &gy, kChainThreads);
+              kRopeMaxRowsPerThread, &gx, &gy);
     a.gate = (const vec16*)gate;
     a.up = (const vec16*)up;
     a.out = (vec16*)gate;
@@ -157,21 +115,9 @@ extern "C" int vvbk_layer_chain(void* hidden, const void* delta, const void* wei
     a.rope_gx = gx;
     a.rope_ctas = gx * gy;
     const size_t per_cta = (size_t)kChainThreads * kChainSwigluUnroll;
-#if VVB_CHAIN_TAIL_UNROLL > 0
-    /* bulk CTAs for all but the last resident wave's worth of vectors, small CTAs for the rest */
-    const size_t wave = (size_t)148 * VVB_CHAIN_CTAS;
-    size_t bulk = a.swiglu_vecs / per_cta;
-    bulk = bulk > wave ? bulk - wave : 0;
-    const size_t per_tail = (size_t)kChainThreads * VVB_CHAIN_TAIL_UNROLL;
-    const size_t swiglu_ctas = bulk + (a.swiglu_vecs - bulk * per_cta + per_tail - 1) / per_tail;
-    a.swiglu_bulk_ctas = (unsigned)bulk;
-#else
     const size_t swiglu_ctas = (a.swiglu_vecs + per_cta - 1) / per_cta;
-    a.swiglu_bulk_ctas = 0;
-#endif
     const size_t total = (size_t)a.norm_ctas + a.rope_ctas + swiglu_ctas;
     if (total > 0x7fffffffu) return (int)cudaErrorNotSupported;
-    a.swiglu_ctas = (unsigned)swiglu_ctas;
     const int guard = row_guard_mode(nvec, kChainNormGroup, kChainNormVPT);
     if (guard == GUARD_NONE)
         launch_pdl(layer_chain_kernel<GUARD_NONE>, dim3((unsigned)total), dim3(kChainThreads), 0, (cudaStream_t)stream, a);

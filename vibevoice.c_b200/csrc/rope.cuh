@@ -68,9 +68,7 @@ __device__ __forceinline__ void sincos_f64(float angle, float* s_out, float* c_o
     *c_out = ((q + 1) & 2) ? -c1 : c1;
 }
 
-/* One CTA's tile: block (bx, by) of the (row tiles, column chunks) grid; THREADS
- * is the CTA size the plan was made for (rope_plan's `threads`). */
-template <int THREADS = kRopeThreads>
+/* One CTA's tile: block (bx, by) of the (row tiles, column chunks) grid. */
 __device__ __forceinline__ void rope_tile_body(const RopeArgs& a, int bx, int by) {
     __shared__ __align__(16) float cos_s[kRopeTableEntries];
     __shared__ __align__(16) float sin_s[kRopeTableEntries];
@@ -83,7 +81,7 @@ __device__ __forceinline__ void rope_tile_body(const RopeArgs& a, int bx, int by
     /* This thread's column, fixed for all its rows. */
     const int slot = t / a.cols_per_cta;
     const int cl = t - slot * a.cols_per_cta;
-    const int c = by * THREADS + cl;
+    const int c = by * kRopeThreads + cl;
     const bool col_ok = (slot < a.row_slots) && (c < a.items_per_row);
     const int head = c / a.hvn;
     const int vec = c - head * a.hvn;
@@ -115,7 +113,7 @@ __device__ __forceinline__ void rope_tile_body(const RopeArgs& a, int bx, int by
 
     /* Phase B: the CTA's cos/sin, once per (row, frequency). */
     const int pos0 = (a.d_position != nullptr ? *a.d_position : a.position_offset) + row0;
-    for (int e = t; e < nrows * a.half; e += THREADS) {
+    for (int e = t; e < nrows * a.half; e += kRopeThreads) {
         const int rl = e / a.half;
         const int i = e - rl * a.half;
         const float ang = __fmul_rn((float)(pos0 + rl), a.inv_freq[i]);
@@ -150,8 +148,7 @@ __device__ __forceinline__ void rope_tile_body(const RopeArgs& a, int bx, int by
  * problem (head_dim a multiple of 16) and return the (x, y) grid. */
 static inline void rope_plan(RopeArgs& a, void* q, void* k, int rows, int n_q_heads, int n_kv_heads,
                              int head_dim, int position_offset, const int* d_position,
-                             const float* inv_freq, int max_passes, unsigned* gx, unsigned* gy,
-                             int threads = kRopeThreads) {
+                             const float* inv_freq, int max_passes, unsigned* gx, unsigned* gy) {
     const int half = head_dim / 2;
     a.q = (vec16*)q;
     a.k = (vec16*)k;
@@ -164,8 +161,8 @@ static inline void rope_plan(RopeArgs& a, void* q, void* k, int rows, int n_q_he
     a.items_per_row = (n_q_heads + n_kv_heads) * a.hvn;
     a.position_offset = position_offset;
     for (int i = 0; i < half; i++) a.inv_freq[i] = inv_freq[i];
-    a.cols_per_cta = a.items_per_row < threads ? a.items_per_row : threads;
-    a.row_slots = threads / a.cols_per_cta;
+    a.cols_per_cta = a.items_per_row < kRopeThreads ? a.items_per_row : kRopeThreads;
+    a.row_slots = kRopeThreads / a.cols_per_cta;
     /* rows per CTA = row_slots * passes, bounded by the cos/sin table */
     int passes = kRopeTableEntries / (half * a.row_slots);
     if (passes > max_passes) passes = max_passes;
@@ -173,12 +170,14 @@ static inline void rope_plan(RopeArgs& a, void* q, void* k, int rows, int n_q_he
         a.row_slots = kRopeTableEntries / half;
         passes = 1;
     }
-    /* Deep grids take the most rows per thread (36.2 us at 14449 rows with 4
-     * against 40.3 with 2 and 55.6 with 1). A grid that fits the SMs in one wave
+    /* Deep grids take the most rows per thread (36.4 us at 14449 rows with 4
+     * against 37.7 with 3, 40.8 with 2 and 55.6 with 1; 11.9 / 12.1 / 13.1 us at
+     * 4096 rows, where the grid is 2.3 waves: fewer rows per thread to even out
+     * the waves costs more than the uneven last wave does). A grid that fits the SMs in one wave
      * is a latency problem instead: it takes the fewest rows per thread that
      * still fit one wave (1.86 against 2.48 us at 64 rows, 4.43 against 5.08 at
      * 1024). kRopeOneWave = 3 CTAs on each of 148 SMs. */
-    const unsigned gy_ = (unsigned)((a.items_per_row + threads - 1) / threads);
+    const unsigned gy_ = (unsigned)((a.items_per_row + kRopeThreads - 1) / kRopeThreads);
     for (int p = 1; p < passes; p++) {
         const unsigned ctas = (unsigned)((rows + a.row_slots * p - 1) / (a.row_slots * p)) * gy_;
         if (ctas <= kRopeOneWave) { passes = p; break; }

@@ -31,12 +31,23 @@
  * (kv_quant.cu:68-73), and is encoded; V is encoded as it is. The cache write
  * shrinks from 4096 to 2048 bytes per 7B token.
  *
+ * TurboQuant caches (template FMT = KV_TQ4 .. KV_TQ1_5, head_dim 128 only): what
+ * is stored is the reference's rotated and quantized form of each head vector
+ * (tq_kv.cuh; src/cuda/kv_quant.cu:85-120): bytes_per_vec bytes of codes in
+ * [max_len, n_kv_heads * bytes_per_vec] plus one FP16 RMS per vector in
+ * [max_len, n_kv_heads]. A head vector is a warp's work, so the rotated K tile of
+ * a CTA goes through shared memory (as for FP8) and its warps take the tile's
+ * (row, head) vectors in turn; the V CTAs walk their rows a head vector per
+ * warp. Per 7B token the cache write shrinks from 4096 bytes to 528 (4-bit) ..
+ * 208 (1.5-bit).
+ *
  * Paged caches (template PAGED): logical position t = cache_offset + r lands in
  * row page_table[t / 64] * 64 + t % 64 of the pool (cache_row below), for every
  * format; the contiguous instantiations carry no trace of the mapping.
  */
 #include "fp8_kv.cuh"
 #include "rope.cuh"
+#include "tq_kv.cuh"
 
 #include <atomic>
 
@@ -61,7 +72,9 @@ struct RopeAppendArgs {
     const vec16* q_bias;      /* each may be null */
     const vec16* k_bias;
     const vec16* v_bias;
-    const vec16* k_ref;       /* FP8 only: [n_kv_heads * head_dim] FP16 subtracted from K; may be null */
+    const vec16* k_ref;       /* FP8 / TurboQuant: [n_kv_heads * head_dim] FP16 subtracted from K; may be null */
+    __half* k_meta;           /* TurboQuant: [max_len, n_kv_heads] FP16 RMS of each stored K vector */
+    __half* v_meta;
     const int* page_table;    /* may be null: logical position t lives in cache row t */
     int cache_offset;         /* cache row of row 0 (when r.d_position is null) */
     int keep_k;               /* also write the rotated K back in place */
@@ -104,6 +117,39 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
         if (row0v >= a.rows) return;
         const int items = min(kVRowsPerCta, a.rows - row0v) * cols_v;
         const int cache_first_v = (a.d_position != nullptr) ? *a.d_position : A.cache_offset;
+        if constexpr (kv_is_tq(FMT)) {
+            /* a head vector (128 values) per warp: lane L takes values 4L .. 4L+3 */
+            constexpr int BPV = tq_bytes_per_vec(FMT);
+            constexpr int kU = 4;
+            const int warp = t >> 5, lane = t & 31;
+            const int nvecs = min(kVRowsPerCta, a.rows - row0v) * a.n_kv;
+            const uint2* vsrc = reinterpret_cast<const uint2*>(A.v) + (size_t)row0v * a.n_kv * 32;
+            for (int base = warp; base < nvecs; base += (kRopeThreads / 32) * kU) {
+                uint2 x[kU];
+#pragma unroll
+                for (int j = 0; j < kU; j++) {
+                    const int idx = base + j * (kRopeThreads / 32);
+                    if (idx < nvecs) x[j] = __ldcs(vsrc + (size_t)idx * 32 + lane);
+                }
+#pragma unroll
+                for (int j = 0; j < kU; j++) {
+                    const int idx = base + j * (kRopeThreads / 32);
+                    if (idx >= nvecs) continue;           /* warp-uniform */
+                    const int rl = idx / a.n_kv, h = idx - rl * a.n_kv;
+                    uint2 xv = x[j];
+                    if (A.v_bias) {
+                        const uint2 b = __ldg(reinterpret_cast<const uint2*>(A.v_bias) + h * 32 + lane);
+                        xv.x = hadd2_bits(xv.x, b.x);
+                        xv.y = hadd2_bits(xv.y, b.y);
+                    }
+                    const float2 f0 = unpack2(xv.x), f1 = unpack2(xv.y);
+                    float v4[4] = {f0.x, f0.y, f1.x, f1.y};
+                    const size_t at = cache_row(PAGED ? A.page_table : nullptr, cache_first_v + row0v + rl) * a.n_kv + h;
+                    tq_store_vec<FMT>(v4, lane, reinterpret_cast<uint8_t*>(A.v_cache) + at * BPV, A.v_meta + at);
+                }
+            }
+            return;
+        }
         constexpr int kVUnroll = 4;
         for (int base = t; base < items; base += kRopeThreads * kVUnroll) {
             vec16 x[kVUnroll];
@@ -120,8 +166,9 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
                 const int cv = it - rl * cols_v;
                 if (A.v_bias) x[j] = add_bias_vec(x[j], __ldg(A.v_bias + cv));
                 const size_t at = cache_row(PAGED ? A.page_table : nullptr, cache_first_v + row0v + rl) * cols_v + cv;
-                if (FMT == KV_RAW) st_stream(A.v_cache + at, x[j]);
-                else __stcs(reinterpret_cast<uint2*>(A.v_cache) + at, fp8_encode8<FMT>(x[j], nullptr));
+                if constexpr (FMT == KV_RAW) st_stream(A.v_cache + at, x[j]);
+                else if constexpr (!kv_is_tq(FMT))
+                    __stcs(reinterpret_cast<uint2*>(A.v_cache) + at, fp8_encode8<FMT>(x[j], nullptr));
             }
         }
         return;
@@ -175,7 +222,7 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
         dst = A.k_cache + off;
         dst_row_first = cache_first;
         to_cache = true;
-        if (FMT != KV_RAW && A.k_ref != nullptr && col_ok && !staged) {
+        if (FMT != KV_RAW && !kv_is_tq(FMT) && A.k_ref != nullptr && col_ok && !staged) {
             rlo = __ldg(A.k_ref + off);
             rhi = __ldg(A.k_ref + off + a.hvn);
         }
@@ -244,12 +291,15 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
             k_stage[(rl * 2 + 0) * kcols + (c - first_k_col)] = xlo;
             k_stage[(rl * 2 + 1) * kcols + (c - first_k_col)] = xhi;
         } else if (FMT != KV_RAW && to_cache) {
-            /* one byte per element: vector i of the row is 8 bytes at uint2 index i */
-            uint2* d8 = reinterpret_cast<uint2*>(A.k_cache) +
-                        (cache_row(PAGED ? A.page_table : nullptr, dst_row_first + row0 + rl) * stride + (size_t)(dst - A.k_cache));
-            const bool sub = A.k_ref != nullptr;
-            __stcs(d8, fp8_encode8<FMT>(xlo, sub ? &rlo : nullptr));
-            __stcs(d8 + a.hvn, fp8_encode8<FMT>(xhi, sub ? &rhi : nullptr));
+            if constexpr (FMT != KV_RAW && !kv_is_tq(FMT)) {
+                /* one byte per element: vector i of the row is 8 bytes at uint2 index i */
+                uint2* d8 = reinterpret_cast<uint2*>(A.k_cache) +
+                            (cache_row(PAGED ? A.page_table : nullptr, dst_row_first + row0 + rl) * stride + (size_t)(dst - A.k_cache));
+                const bool sub = A.k_ref != nullptr;
+                __stcs(d8, fp8_encode8<FMT>(xlo, sub ? &rlo : nullptr));
+                __stcs(d8 + a.hvn, fp8_encode8<FMT>(xhi, sub ? &rhi : nullptr));
+            }
+            /* (a TurboQuant launch always stages: the launcher plans the tile to fit) */
         } else {
             const size_t drow = to_cache ? cache_row(PAGED ? A.page_table : nullptr, dst_row_first + row0 + rl)
                                          : (size_t)(row0 + rl);
@@ -269,7 +319,32 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
      * which would finish long after the others. The staged K tile is therefore
      * encoded by ALL threads, one 16-byte vector (8 bytes out) at a time;
      * consecutive threads write consecutive 8-byte pieces of a cache row. */
-    if (FMT != KV_RAW && staged) {
+    if constexpr (kv_is_tq(FMT)) {
+        if (staged) {
+            __syncthreads();
+            constexpr int BPV = tq_bytes_per_vec(FMT);
+            const int warp = t >> 5, lane = t & 31;
+            const int heads = kcols / a.hvn;                       /* K heads of this column chunk */
+            const int head0 = first_k_col / a.hvn - a.n_q;         /* first of them, as a KV head index */
+            /* lane L's values 4L .. 4L+3: half (d >= 64), vector inside the half, first or second 8 bytes of it */
+            const int half_sel = lane >> 4, vsel = (lane & 15) >> 1, part = lane & 1;
+            for (int idx = warp; idx < nrows * heads; idx += kRopeThreads / 32) {
+                const int rl = idx / heads, hk = idx - rl * heads;
+                const uint2 raw = reinterpret_cast<const uint2*>(&k_stage[(rl * 2 + half_sel) * kcols + hk * a.hvn + vsel])[part];
+                float2 f0 = unpack2(raw.x), f1 = unpack2(raw.y);
+                const int h = head0 + hk;
+                if (A.k_ref != nullptr) {
+                    const uint2 r = __ldg(reinterpret_cast<const uint2*>(A.k_ref) + h * 32 + lane);
+                    const float2 r0 = unpack2(r.x), r1 = unpack2(r.y);
+                    f0.x = __fsub_rn(f0.x, r0.x); f0.y = __fsub_rn(f0.y, r0.y);
+                    f1.x = __fsub_rn(f1.x, r1.x); f1.y = __fsub_rn(f1.y, r1.y);
+                }
+                float v4[4] = {f0.x, f0.y, f1.x, f1.y};
+                const size_t at = cache_row(PAGED ? A.page_table : nullptr, cache_first + row0 + rl) * a.n_kv + h;
+                tq_store_vec<FMT>(v4, lane, reinterpret_cast<uint8_t*>(A.k_cache) + at * BPV, A.k_meta + at);
+            }
+        }
+    } else if (FMT != KV_RAW && staged) {
         __syncthreads();
         const size_t stride_k = (size_t)a.n_kv * vph;
         for (int idx = t; idx < nrows * 2 * kcols; idx += kRopeThreads) {
@@ -306,16 +381,29 @@ extern "C" int vvbk_rope_append(void* q, void* k, const void* v,
                                 int rows, int n_q_heads, int n_kv_heads, int head_dim,
                                 int position_offset, int cache_offset, const int* d_position,
                                 const float* inv_freq, int keep_k, int kv_format, const void* k_ref,
-                                const int* page_table, void* stream) {
-    if (kv_format < KV_RAW || kv_format > KV_E5M2 || !aligned16(k_ref)) return (int)cudaErrorNotSupported;
+                                const int* page_table, void* k_meta, void* v_meta, void* stream) {
+    if (kv_format < KV_RAW || kv_format > KV_TQ1_5 || !aligned16(k_ref)) return (int)cudaErrorNotSupported;
+    const bool tq = kv_is_tq(kv_format);
+    if (tq && (head_dim != 128 || k_meta == nullptr || v_meta == nullptr || n_kv_heads > 32 ||
+               (reinterpret_cast<uintptr_t>(k_meta) & 1u) || (reinterpret_cast<uintptr_t>(v_meta) & 1u)))
+        return (int)cudaErrorNotSupported;
     if (head_dim % 16 != 0 || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(q_bias) ||
         !aligned16(k_bias) || !aligned16(v_bias) || !aligned16(k_cache) || !aligned16(v_cache))
         return (int)cudaErrorNotSupported;
     RopeAppendArgs A;
     unsigned gx, gy;
     /* tiles over the Q and K heads; one more grid row (the first) carries V */
+    /* TurboQuant: the CTA's rotated K tile (its K columns x 2 halves x its rows) must fit the
+     * 512-vector staging buffer, which bounds the rows a CTA takes */
+    int max_passes = kRopeMaxRowsPerThread;
+    if (tq) {
+        const int kcols = n_kv_heads * (head_dim / 16);          /* <= 256: one column chunk holds them all */
+        const int fit = 512 / (2 * kcols);
+        if (fit < 1) return (int)cudaErrorNotSupported;
+        if (max_passes > fit) max_passes = fit;
+    }
     rope_plan(A.r, q, k, rows, n_q_heads, n_kv_heads, head_dim, position_offset, d_position, inv_freq,
-              kRopeMaxRowsPerThread, &gx, &gy);
+              max_passes, &gx, &gy);
     const unsigned gx_v = (unsigned)((rows + kVRowsPerCta - 1) / kVRowsPerCta);
     if (gx_v > gx) gx = gx_v;
     gy += 1;
@@ -326,6 +414,8 @@ extern "C" int vvbk_rope_append(void* q, void* k, const void* v,
     A.k_bias = (const vec16*)k_bias;
     A.v_bias = (const vec16*)v_bias;
     A.k_ref = (kv_format == KV_RAW) ? nullptr : (const vec16*)k_ref;
+    A.k_meta = (__half*)k_meta;
+    A.v_meta = (__half*)v_meta;
     A.page_table = page_table;
     A.cache_offset = cache_offset;
     A.keep_k = keep_k;
@@ -333,15 +423,23 @@ extern "C" int vvbk_rope_append(void* q, void* k, const void* v,
     const dim3 grid(gx, gy), block(kRopeThreads);
     cudaStream_t s = (cudaStream_t)stream;
     /* the paged mapping is a template parameter so that the contiguous cache pays nothing for it */
-    if (page_table == nullptr) {
-        if (kv_format == KV_E4M3) launch_pdl(rope_append_kernel<KV_E4M3, false>, grid, block, 0, s, A);
-        else if (kv_format == KV_E5M2) launch_pdl(rope_append_kernel<KV_E5M2, false>, grid, block, 0, s, A);
-        else launch_pdl(rope_append_kernel<KV_RAW, false>, grid, block, 0, s, A);
-    } else {
-        if (kv_format == KV_E4M3) launch_pdl(rope_append_kernel<KV_E4M3, true>, grid, block, 0, s, A);
-        else if (kv_format == KV_E5M2) launch_pdl(rope_append_kernel<KV_E5M2, true>, grid, block, 0, s, A);
-        else launch_pdl(rope_append_kernel<KV_RAW, true>, grid, block, 0, s, A);
+#define VVB_APPEND_CASE(F)                                                                          \
+    case F:                                                                                         \
+        if (page_table == nullptr) launch_pdl(rope_append_kernel<F, false>, grid, block, 0, s, A);  \
+        else launch_pdl(rope_append_kernel<F, true>, grid, block, 0, s, A);                         \
+        break;
+    switch (kv_format) {
+        VVB_APPEND_CASE(KV_E4M3)
+        VVB_APPEND_CASE(KV_E5M2)
+        VVB_APPEND_CASE(KV_TQ4)
+        VVB_APPEND_CASE(KV_TQ3)
+        VVB_APPEND_CASE(KV_TQ2)
+        VVB_APPEND_CASE(KV_TQ1_5)
+        default:
+            if (page_table == nullptr) launch_pdl(rope_append_kernel<KV_RAW, false>, grid, block, 0, s, A);
+            else launch_pdl(rope_append_kernel<KV_RAW, true>, grid, block, 0, s, A);
     }
+#undef VVB_APPEND_CASE
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }

@@ -136,7 +136,7 @@ __device__ __forceinline__ vec16 scale_row_vec(const vec16& h, const vec16& w, f
  * thread. (Keeping the row widened to float across the reduction, to save the
  * second widening, was measured: same registers after the compiler's own
  * choices, same time.) */
-template <int VPT, int GROUPS, int GUARD, bool LATEW = false>
+template <int VPT, int GROUPS, int GUARD, bool LATEW = false, int DELTA = 2>
 __device__ __forceinline__ void row_norm_produce(const RowNormArgs& a, int row, int t, int G, int grp,
                                                  vec16 (&yv)[VPT]) {
     __shared__ double red[GROUPS][32];
@@ -157,7 +157,8 @@ __device__ __forceinline__ void row_norm_produce(const RowNormArgs& a, int row, 
         srow = (size_t)id;
     }
     const vec16* sp = a.src + srow * (size_t)a.nvec + t;
-    const bool has_delta = (a.delta != nullptr);
+    /* DELTA: 0 no addend (its registers are not even reserved), 1 an addend, 2 decided by the argument */
+    const bool has_delta = (DELTA == 2) ? (a.delta != nullptr) : (DELTA == 1);
 
     /* Every load of the row, the addend and gamma goes out before any is used. */
     vec16 hv[VPT], dv[VPT], wv[VPT];
@@ -176,11 +177,18 @@ __device__ __forceinline__ void row_norm_produce(const RowNormArgs& a, int row, 
      * and does not pay: 62.5 against 62.2 us, the chain 328.2 against 326.1 --
      * their addresses are known at once, so the loads are already in flight.) */
 
-    /* the new hidden state, rounded to FP16 (== widen, add, narrow: see
-     * hadd2_bits); the norm sees the rounded values */
-    if (has_delta) {
+    double ss = 0.0, ss1 = 0.0;
 #pragma unroll
-        for (int j = 0; j < VPT; j++) hv[j] = hadd8(hv[j], dv[j]);
+    for (int j = 0; j < VPT; j++) {
+        uint32_t* hw = reinterpret_cast<uint32_t*>(&hv[j]);
+        const uint32_t* dw = reinterpret_cast<const uint32_t*>(&dv[j]);
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            if (has_delta) hw[e] = hadd2_bits(hw[e], dw[e]);
+            const float2 f = unpack2(hw[e]);
+            ss = fma((double)f.x, (double)f.x, ss);
+            ss1 = fma((double)f.y, (double)f.y, ss1);
+        }
     }
     if (a.row_out != nullptr) {
         vec16* rp = a.row_out + roff + t;
@@ -189,18 +197,6 @@ __device__ __forceinline__ void row_norm_produce(const RowNormArgs& a, int row, 
             if (VVB_ROW_IN(j)) st_stream(rp + j * G, hv[j]);
     }
 #undef VVB_ROW_IN
-    /* two accumulators: the chain of dependent double FMAs is half as long */
-    double ss = 0.0, ss1 = 0.0;
-#pragma unroll
-    for (int j = 0; j < VPT; j++) {
-        const uint32_t* hw = reinterpret_cast<const uint32_t*>(&hv[j]);
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            const float2 f = unpack2(hw[e]);
-            ss = fma((double)f.x, (double)f.x, ss);
-            ss1 = fma((double)f.y, (double)f.y, ss1);
-        }
-    }
     ss += ss1;
 
     ss = warp_sum(ss);
@@ -210,10 +206,9 @@ __device__ __forceinline__ void row_norm_produce(const RowNormArgs& a, int row, 
     } else {
         asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "r"(G) : "memory");
     }
-    /* The scalar tail (a double division, a square root and a float division:
-     * ~130 instructions) is issued by ONE warp of the group, not by all of
-     * them: with 32 elements per thread, every warp repeating it would cost a
-     * third of the kernel's instruction issue. */
+    /* The scalar tail (the mean, a square root and a float division: some forty
+     * dependent instructions) is issued by ONE warp of the group, not by all of
+     * them. */
     if (t < 32) {
         double s = (t < (G >> 5)) ? red[grp][t] : 0.0;
         s = warp_sum(s);
@@ -233,10 +228,10 @@ __device__ __forceinline__ void row_norm_produce(const RowNormArgs& a, int row, 
 }
 
 /* One row: produce, then stream the normalised row out. */
-template <int VPT, int GROUPS, int GUARD>
+template <int VPT, int GROUPS, int GUARD, bool LATEW = false, int DELTA = 2>
 __device__ __forceinline__ void row_norm_body(const RowNormArgs& a, int row, int t, int G, int grp) {
     vec16 yv[VPT];
-    row_norm_produce<VPT, GROUPS, GUARD>(a, row, t, G, grp, yv);
+    row_norm_produce<VPT, GROUPS, GUARD, LATEW, DELTA>(a, row, t, G, grp, yv);
     if (GROUPS > 1 && row >= a.rows) return;
     vec16* np_ = a.normed + (size_t)row * (size_t)a.nvec + t;
 #pragma unroll

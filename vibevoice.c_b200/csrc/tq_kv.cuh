@@ -1,0 +1,201 @@
+/*
+ * tq_kv.cuh -- the reference's TurboQuant encodings of the KV cache
+ * (include/vibevoice/kv_quant.h:37-40: VV_KV_TQ4 = 3, TQ3 = 4, TQ2 = 5,
+ * TQ1_5 = 6; the stored bits are defined by src/cuda/kv_quant.cu:40-121 and
+ * src/cuda/kv_codec.cuh:42-62,133-163,232-291), one 128-wide head vector per
+ * warp.
+ *
+ * A stored vector is its randomized Hadamard transform, quantized against its
+ * own RMS:
+ *   v[d]  = value - reference key (float), times a fixed +-1 hashed from d;
+ *   v     = WHT128(v) / sqrt(128): lane L of the warp holds v[4L .. 4L+3], two
+ *           butterfly stages run inside the lane and five across lanes;
+ *   sigma = sqrt(max(sum(v^2) / 128, 1e-12)), kept as FP16 beside the codes;
+ *   code  = per value, how many of the format's decision thresholds
+ *           v / sigma exceeds (4 / 3 / 2 bits); the 1.5-bit format codes pairs
+ *           by the nearest of eight 2-D code words (3 bits a pair);
+ *   lane L's codes are bits [nb*L, nb*(L+1)) of the vector, little endian.
+ *
+ * The reference builds with fast-math, so its square root, its 1 / sigma (which
+ * the compiler turns into a reciprocal square root of the mean square) and its
+ * division by head_dim are the hardware approximations; this file names the
+ * same PTX instructions (sqrt.approx.ftz, rsqrt.approx.ftz, div.approx.ftz)
+ * and performs every other operation in the reference's order, so the bytes
+ * are those of the reference's kernel on the same GPU (tests/test_tq_kv.py
+ * compares them with the live kernel). The code books are the format's
+ * definition -- Lloyd-Max levels of a unit Gaussian -- and have to be these
+ * numbers for a stored cache to be readable by the reference's attention
+ * kernels.
+ */
+#pragma once
+#include "vvb_device.cuh"
+
+namespace vvb {
+
+enum { KV_TQ4 = 3, KV_TQ3 = 4, KV_TQ2 = 5, KV_TQ1_5 = 6 };
+
+template <int FMT> struct TqBits { static constexpr int N = 0; };
+template <> struct TqBits<KV_TQ4> { static constexpr int N = 16; };      /* bits per lane: 4 values x 4 */
+template <> struct TqBits<KV_TQ3> { static constexpr int N = 12; };
+template <> struct TqBits<KV_TQ2> { static constexpr int N = 8; };
+template <> struct TqBits<KV_TQ1_5> { static constexpr int N = 6; };
+__host__ __device__ constexpr bool kv_is_tq(int fmt) { return fmt >= KV_TQ4 && fmt <= KV_TQ1_5; }
+__host__ __device__ constexpr int tq_bytes_per_vec(int fmt) {
+    return fmt == KV_TQ4 ? 64 : fmt == KV_TQ3 ? 48 : fmt == KV_TQ2 ? 32 : fmt == KV_TQ1_5 ? 24 : 0;
+}
+
+constexpr float kTqWhtNorm = 0.0883883476f;      /* 1 / sqrt(128) as the reference's float constant */
+
+__device__ __forceinline__ float tq_sign(int d) {
+    uint32_t h = (uint32_t)d * 2654435761u + 0x9E3779B9u;
+    h ^= h >> 15;
+    h *= 0x85EBCA6Bu;
+    h ^= h >> 13;
+    return (h & 1u) ? -1.0f : 1.0f;
+}
+
+/* The levels (src/cuda/kv_codec.cuh:46-62). Scalar formats compare against the
+ * decision thresholds 0.5f * (level[j] + level[j + 1]), which the reference forms
+ * in float at run time; as compile-time constants they are the same floats (one
+ * rounded addition, one exact halving) and become immediates of the compares. */
+__host__ __device__ constexpr float tq_lev4(int j) {
+    constexpr float v[16] = {-2.725112f, -2.065280f, -1.613787f, -1.251845f, -0.938657f, -0.654379f,
+                             -0.386970f, -0.127960f, +0.127960f, +0.386970f, +0.654379f, +0.938657f,
+                             +1.251845f, +1.613787f, +2.065280f, +2.725112f};
+    return v[j];
+}
+__host__ __device__ constexpr float tq_lev3(int j) {
+    constexpr float v[8] = {-2.150300f, -1.343258f, -0.755588f, -0.244756f,
+                            +0.244756f, +0.755588f, +1.343258f, +2.150300f};
+    return v[j];
+}
+__host__ __device__ constexpr float tq_lev2(int j) {
+    constexpr float v[4] = {-1.511418f, -0.452456f, +0.452456f, +1.511418f};
+    return v[j];
+}
+/* the 1.5-bit format's eight 2-D code words, (first, second) coordinate interleaved */
+__host__ __device__ constexpr float tq_vq15(int j) {
+    constexpr float v[16] = {-1.500251f, +0.674678f, -1.127883f, -0.787015f, -0.283251f, +0.390133f,
+                             -0.103102f, +1.624620f, +0.100120f, -1.618563f, +0.286482f, -0.379555f,
+                             +1.134227f, +0.790368f, +1.496572f, -0.666578f};
+    return v[j];
+}
+template <int FMT>
+__host__ __device__ constexpr float tq_threshold(int j) {
+    return FMT == KV_TQ4 ? 0.5f * (tq_lev4(j) + tq_lev4(j + 1))
+         : FMT == KV_TQ3 ? 0.5f * (tq_lev3(j) + tq_lev3(j + 1))
+                         : 0.5f * (tq_lev2(j) + tq_lev2(j + 1));
+}
+
+/* 128-point Walsh-Hadamard transform over a warp, four values per lane: strides
+ * 1 and 2 inside the lane, strides 4 .. 64 against lane ^ 1 .. lane ^ 16; the
+ * lane with the stride's bit set keeps (other - own), the other (own + other). */
+__device__ __forceinline__ void tq_wht128(float (&v)[4], int lane) {
+    float a;
+    a = __fadd_rn(v[0], v[1]); v[1] = __fsub_rn(v[0], v[1]); v[0] = a;
+    a = __fadd_rn(v[2], v[3]); v[3] = __fsub_rn(v[2], v[3]); v[2] = a;
+    a = __fadd_rn(v[0], v[2]); v[2] = __fsub_rn(v[0], v[2]); v[0] = a;
+    a = __fadd_rn(v[1], v[3]); v[3] = __fsub_rn(v[1], v[3]); v[1] = a;
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+        const bool upper = (lane & m) != 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float o = __shfl_xor_sync(0xffffffffu, v[i], m);
+            v[i] = upper ? __fsub_rn(o, v[i]) : __fadd_rn(v[i], o);
+        }
+    }
+}
+
+__device__ __forceinline__ float tq_sqrt_approx(float x) {
+    float r;
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float tq_rsqrt_approx(float x) {
+    float r;
+    asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float tq_div_approx(float x, float y) {
+    float r;
+    asm("div.approx.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(x), "f"(y));
+    return r;
+}
+
+/* Codes of a lane's four values. */
+template <int FMT>
+__device__ __forceinline__ uint32_t tq_pack4(const float (&y)[4], float inv_sigma) {
+    uint32_t bits = 0;
+    if (FMT == KV_TQ1_5) {
+#pragma unroll
+        for (int p = 0; p < 2; p++) {
+            const float a = __fmul_rn(y[2 * p], inv_sigma), b = __fmul_rn(y[2 * p + 1], inv_sigma);
+            uint32_t best = 0;
+            float bd = 3.402823466e+38f;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const float da = __fsub_rn(a, tq_vq15(2 * c)), db = __fsub_rn(b, tq_vq15(2 * c + 1));
+                const float d = __fmaf_rn(da, da, __fmul_rn(db, db));
+                if (d < bd) { bd = d; best = (uint32_t)c; }
+            }
+            bits |= best << (3 * p);
+        }
+        return bits;
+    }
+    constexpr int W = (FMT == KV_TQ4) ? 4 : (FMT == KV_TQ3) ? 3 : 2;
+    constexpr int NLEV = 1 << W;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float t = __fmul_rn(y[i], inv_sigma);
+        uint32_t c = 0;
+#pragma unroll
+        for (int j = 0; j + 1 < NLEV; j++) c += (t > tq_threshold<FMT>(j)) ? 1u : 0u;
+        bits |= c << (W * i);
+    }
+    return bits;
+}
+
+/* One head vector, a warp: lane holds the four values x[4*lane ..] (already
+ * minus the reference key). Writes bytes_per_vec bytes at `dst` (4-byte
+ * aligned) and the FP16 sigma at `meta`. Every lane of the warp must call. */
+template <int FMT>
+__device__ __forceinline__ void tq_store_vec(float (&v)[4], int lane, uint8_t* dst, __half* meta) {
+    constexpr int NB = TqBits<FMT>::N;
+    const int d0 = lane * 4;
+#pragma unroll
+    for (int i = 0; i < 4; i++) v[i] = __fmul_rn(v[i], tq_sign(d0 + i));
+    tq_wht128(v, lane);
+#pragma unroll
+    for (int i = 0; i < 4; i++) v[i] = __fmul_rn(v[i], kTqWhtNorm);
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) ss = __fmaf_rn(v[i], v[i], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+    /* sigma (stored) is the approximate square root of the mean square; the scale the codes
+     * are taken against is the approximate RECIPROCAL square root of that same mean -- what the
+     * reference's fast-math build makes of 1.0f / sigma -- not a reciprocal of sigma: the two
+     * differ in the last bit often enough to move a code once in some 10^4 vectors. */
+    const float mean_sq = fmaxf(tq_div_approx(ss, 128.0f), 1e-12f);
+    const float sigma = tq_sqrt_approx(mean_sq);
+    const uint32_t bits = tq_pack4<FMT>(v, tq_rsqrt_approx(mean_sq));
+
+    /* Word w of the vector holds bits [32w, 32w + 32): lanes floor(32w / NB) ..
+     * floor((32w + 31) / NB). Lane w (< words) gathers them with shuffles. */
+    constexpr int WORDS = NB;                         /* 32 lanes * NB bits / 32 */
+    constexpr int SPAN = (32 + NB - 1) / NB + 1;       /* lanes that can touch one word */
+    const int first = (32 * lane) / NB;                /* for lane = word index */
+    uint32_t word = 0;
+#pragma unroll
+    for (int k = 0; k < SPAN; k++) {
+        const int src = first + k;
+        const uint32_t b = __shfl_sync(0xffffffffu, bits, src & 31);
+        const int shift = NB * src - 32 * lane;        /* where that lane's bits begin, relative to this word */
+        if (src < 32 && shift < 32) word |= (shift >= 0) ? (b << shift) : (b >> (-shift));
+    }
+    if (lane < WORDS) reinterpret_cast<uint32_t*>(dst)[lane] = word;
+    if (lane == 0) *meta = __float2half_rn(sigma);
+}
+
+}  // namespace vvb

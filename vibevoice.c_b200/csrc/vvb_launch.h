@@ -39,14 +39,16 @@ int vvbk_rope(void* q, void* k, int rows, int n_q_heads, int n_kv_heads, int hea
  * reference's software FP8 E4M3 / E5M2 bytes (one per element); k_ref (FP8
  * only, may be null): FP16 [n_kv_heads * head_dim] subtracted from K first.
  * page_table (may be null): device ints, one per 64-position page of the
- * logical sequence, giving the page's index in the cache arrays. */
+ * logical sequence, giving the page's index in the cache arrays. kv_format
+ * 3..6: the TurboQuant formats (head_dim 128 only); k_meta / v_meta then receive
+ * one FP16 RMS per stored vector, [max_len, n_kv_heads]. */
 int vvbk_rope_append(void* q, void* k, const void* v,
                      const void* q_bias, const void* k_bias, const void* v_bias,
                      void* k_cache, void* v_cache,
                      int rows, int n_q_heads, int n_kv_heads, int head_dim,
                      int position_offset, int cache_offset, const int* d_position,
                      const float* inv_freq, int keep_k, int kv_format, const void* k_ref,
-                     const int* page_table, void* stream);
+                     const int* page_table, void* k_meta, void* v_meta, void* stream);
 
 /* SwiGLU (csrc/swiglu.cu). Flat: gate/up/out of n elements. Fused: rows of
  * [gate | up] with 2*inter halves per row. */

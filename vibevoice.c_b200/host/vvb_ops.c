@@ -71,9 +71,11 @@ vv_status_t vvb_kv_append_dev(const vvb_kv_append_t* a, void* stream) {
     /* the reference's vv_kv_format_t: 0 FP16, 1 FP8 E4M3, 2 FP8 E5M2 (its own
      * FP8 store takes head_dim 128 only, src/cuda/kv_quant.cu:527; the byte
      * layout is defined for any head_dim and this kernel takes multiples of
-     * 16). The TurboQuant formats (3..6) are not written by this library. */
-    if (a->kv_format != VVB_KV_FP16 && a->kv_format != VVB_KV_FP8_E4M3 && a->kv_format != VVB_KV_FP8_E5M2)
-        return VV_ERR_UNSUPPORTED;
+     * 16); 3..6 the TurboQuant formats, defined for head_dim 128. */
+    if (a->kv_format < VVB_KV_FP16 || a->kv_format > VVB_KV_TQ1_5) return VV_ERR_UNSUPPORTED;
+    const int tq = a->kv_format >= VVB_KV_TQ4;
+    if (tq && (!a->k_meta || !a->v_meta)) return VV_ERR_NULL_PTR;
+    if (tq && a->head_dim != 128) return VV_ERR_UNSUPPORTED;       /* as the reference's store: src/cuda/kv_quant.cu:527 */
     if (a->rows == 0) return VV_OK;
     if (a->head_dim / 2 > VVB_ROPE_MAX_HALF) return VV_ERR_UNSUPPORTED;
     float inv_freq[VVB_ROPE_MAX_HALF];
@@ -81,7 +83,8 @@ vv_status_t vvb_kv_append_dev(const vvb_kv_append_t* a, void* stream) {
     const int err = vvbk_rope_append(a->q, a->k, a->v, a->q_bias, a->k_bias, a->v_bias, a->k_store, a->v_store,
                                      a->rows, a->n_q_heads, a->n_kv_heads, a->head_dim, a->position_offset,
                                      a->cache_offset, a->d_position, inv_freq, a->keep_k, a->kv_format,
-                                     a->kv_format == VVB_KV_FP16 ? NULL : a->k_ref, a->page_table, stream);
+                                     a->kv_format == VVB_KV_FP16 ? NULL : a->k_ref, a->page_table,
+                                     tq ? a->k_meta : NULL, tq ? a->v_meta : NULL, stream);
     if (err == 801) return VV_ERR_UNSUPPORTED;   /* cudaErrorNotSupported: not vectorisable */
     return from_cuda(err);
 }
@@ -94,7 +97,7 @@ static vv_status_t rope_qk_append(void* q, void* k, const void* v,
                                   float theta, int kv_format, int keep_k, void* stream) {
     const vvb_kv_append_t a = {q, k, v, q_bias, k_bias, v_bias, k_cache, v_cache, k_ref, NULL, d_position,
                                rows, n_q_heads, n_kv_heads, head_dim, position_offset, cache_offset,
-                               theta, kv_format, keep_k};
+                               theta, kv_format, keep_k, NULL, NULL};
     return vvb_kv_append_dev(&a, stream);
 }
 

@@ -66,6 +66,7 @@ class KvAppend(C.Structure):
         ("k_store", _vp), ("v_store", _vp), ("k_ref", _vp), ("page_table", _vp), ("d_position", _vp),
         ("rows", _i), ("n_q_heads", _i), ("n_kv_heads", _i), ("head_dim", _i),
         ("position_offset", _i), ("cache_offset", _i), ("theta", _f), ("kv_format", _i), ("keep_k", _i),
+        ("k_meta", _vp), ("v_meta", _vp),
     ]
 
 
@@ -275,15 +276,16 @@ def vvb_rope_qk_append_dev(q, k, v, q_bias, k_bias, v_bias, k_cache, v_cache, ro
 
 
 VVB_KV_FP16, VVB_KV_FP8_E4M3, VVB_KV_FP8_E5M2 = 0, 1, 2
+VVB_KV_TQ4, VVB_KV_TQ3, VVB_KV_TQ2, VVB_KV_TQ1_5 = 3, 4, 5, 6
 
 
 def vvb_kv_append_dev(q, k, v, k_store, v_store, rows, n_q_heads, n_kv_heads, head_dim, *, q_bias=None, k_bias=None,
                       v_bias=None, k_ref=None, page_table=None, d_position=None, position_offset=0, cache_offset=0,
-                      theta=1e6, kv_format=0, keep_k=0, stream=None) -> int:
-    """Bias adds + RoPE + KV-cache append (FP16 or FP8, contiguous or paged) in one launch."""
+                      theta=1e6, kv_format=0, keep_k=0, k_meta=None, v_meta=None, stream=None) -> int:
+    """Bias adds + RoPE + KV-cache append (FP16, FP8 or TurboQuant; contiguous or paged) in one launch."""
     a = KvAppend(_ptr(q), _ptr(k), _ptr(v), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias), _ptr(k_store), _ptr(v_store),
                  _ptr(k_ref), _ptr(page_table), _ptr(d_position), rows, n_q_heads, n_kv_heads, head_dim,
-                 position_offset, cache_offset, theta, kv_format, keep_k)
+                 position_offset, cache_offset, theta, kv_format, keep_k, _ptr(k_meta), _ptr(v_meta))
     return _lib.vvb_kv_append_dev(C.byref(a), _stream(stream))
 
 
