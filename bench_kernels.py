@@ -220,6 +220,16 @@ def run(peak_gbs: float, peak_kind: str, only=None, plain=False):
                                                           HD, 0, 0, None, 1e6, vv.VVB_KV_FP8_E4M3, 0, s)),
            rows * (NQ + 2 * NKV) * HD * 2 + rows * 2 * NKV * HD,
            rows * (2 * NQ + 2 * NKV) * HD * 2 + rows * 2 * NKV * HD)
+    # and for the TurboQuant caches (4-bit and 1.5-bit): codes + one FP16 RMS per head vector
+    for fmt, fname, bpv in ((vv.VVB_KV_TQ4, "tq4", 64), (vv.VVB_KV_TQ1_5, "tq1_5", 24)):
+        R.case(f"rope_qk_append_{fname} [14449,28+4+4,128] with biases, reference key", None,
+               lambda: (rn(rows, NQ, HD), rn(rows, NKV, HD), rn(rows, NKV, HD), u8(rows, NKV * bpv), u8(rows, NKV * bpv),
+                        f16(rows, NKV), f16(rows, NKV)),
+               lambda b, s: _ok(vv.vvb_kv_append_dev(b[0], b[1], b[2], b[3], b[4], rows, NQ, NKV, HD, q_bias=bq, k_bias=bk,
+                                                     v_bias=bv, k_ref=kref, theta=1e6, kv_format=fmt, k_meta=b[5],
+                                                     v_meta=b[6], stream=s)),
+               rows * (NQ + 2 * NKV) * HD * 2 + rows * 2 * NKV * (bpv + 2),
+               rows * (2 * NQ + 2 * NKV) * HD * 2 + rows * 2 * NKV * (bpv + 2))
 
     # int8 activation quantizers at long-prompt prefill size (14449 rows), with run sums
     def qbufs(K):

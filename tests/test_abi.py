@@ -133,6 +133,14 @@ def test_argument_validation_needs_no_gpu(vv):
     assert vv.vvb_embedding_rmsnorm_dev(P, P, P, None, P, 1, 8, 10, 1e-6, stream=0) == vv.VV_ERR_NULL_PTR
     assert vv._lib.vvb_layer_chain_dev(None, 0) == vv.VV_ERR_NULL_PTR
     assert vv._lib.vvb_layer_chain_host(None, None) == vv.VV_ERR_NULL_PTR
+    assert vv._lib.vvb_layer_chain_host_multi(None, None) == vv.VV_ERR_NULL_PTR
+    import ctypes as C
+    m = C.c_void_p()
+    assert vv._lib.vvb_host_multi_create(None, None, 2, 64, 3584, 28, 4, 128, 18944) == vv.VV_ERR_NULL_PTR
+    assert vv._lib.vvb_host_multi_create(C.byref(m), None, 0, 64, 3584, 28, 4, 128, 18944) == vv.VV_ERR_INVALID_ARG
+    assert vv._lib.vvb_host_multi_create(C.byref(m), None, 65, 64, 3584, 28, 4, 128, 18944) == vv.VV_ERR_INVALID_ARG
+    assert vv._lib.vvb_host_multi_devices(None) == 0 and vv._lib.vvb_host_multi_last_ms(None) == 0.0
+    vv._lib.vvb_host_multi_destroy(None)                 # a no-op, like free(NULL)
     # the fused KV-cache append, in its three forms
     assert vv._lib.vvb_kv_append_dev(None, 0) == vv.VV_ERR_NULL_PTR
     kv = lambda **kw: vv.vvb_kv_append_dev(kw.pop("q", P), kw.pop("k", P), P, kw.pop("ks", P), P, kw.pop("rows", 1),

@@ -353,7 +353,8 @@ def test_chain_equals_separate_calls(vv, rows, H, nq, nkv, hd, inter, expect_lau
 # --------------------------------------------------------------- shapes and edges
 @pytest.mark.parametrize("rows,hidden", [(1, 3584), (3, 3584), (513, 3584), (2000, 3584), (7, 1536), (1300, 1536),
                                           (5, 256), (4, 128), (3, 8), (2, 3592), (3, 250), (2, 7), (1, 1),
-                                          (2, 16384), (2, 20000), (1500, 512), (1200, 4096)])
+                                          (2, 16384), (2, 20000), (1500, 512), (1200, 4096),
+                                          (700, 2048), (700, 2560), (700, 3072), (700, 4608), (5000, 3584)])
 def test_add_rmsnorm_shapes(vv, orc, rows, hidden):
     rng = np.random.default_rng(rows * 100003 + hidden)
     h, d = randn16(rng, rows, hidden), randn16(rng, rows, hidden)

@@ -81,6 +81,84 @@ __device__ __forceinline__ uint32_t transpose4(uint32_t v, int i) {
     return (i & 1) ? __byte_perm(y, v, 0x7351) : __byte_perm(v, y, 0x6240);
 }
 
+/* Quantizes and stores the VPT vectors a thread holds (vector v = t + j*G covers
+ * columns 8v .. 8v+7: chunk i = v & 3 of run v >> 2; four consecutive threads
+ * hold the four chunks of a run -- G is a multiple of 32 -- which is what the
+ * per-run sum and the interleaved layouts need). */
+template <int VPT, int GUARD, int LAYOUT, bool SUMS>
+__device__ __forceinline__ void quantize_vectors(const vec16 (&yv)[VPT], float inv, int t, int G, int nvec,
+                                                 int8_t* xq, int32_t* xsum) {
+    const float2 inv2 = splat2(inv);
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        const int v = t + j * G;
+        const bool ok = vec_inside<VPT, GUARD>(j, v, nvec);
+        /* round-half-even without the conversion unit: p = v*inv is rounded
+         * to float first (as the CPU does) and adding 1.5*2^23 rounds it to an
+         * integer in the float adder's nearest-even mode; the low byte of the
+         * sum's bit pattern is then q as a signed byte (the constant's low
+         * byte is zero). The reference's clamp to +-127 can never act: amax is
+         * the exact maximum of |v|, so |p| <= amax * fl(127/amax) <
+         * 127.00002 and rounds to at most 127. (Rows holding an infinity or
+         * a NaN have no defined quantization on the CPU path either.) */
+        uint32_t rb[8];
+        const uint32_t* yw = reinterpret_cast<const uint32_t*>(&yv[j]);
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            /* two columns per packed multiply; the adds stay scalar: the
+             * assembler merges a packed multiply and a packed add into one
+             * fused multiply-add even when both name .rn, which skips the
+             * rounding of the product and moves ties */
+            const float2 p = mul2(unpack2(yw[e]), inv2);
+            rb[2 * e] = __float_as_uint(__fadd_rn(p.x, 12582912.0f));
+            rb[2 * e + 1] = __float_as_uint(__fadd_rn(p.y, 12582912.0f));
+        }
+        const uint32_t lo = __byte_perm(__byte_perm(rb[0], rb[1], 0x0040), __byte_perm(rb[2], rb[3], 0x0040), 0x5410);
+        const uint32_t hi = __byte_perm(__byte_perm(rb[4], rb[5], 0x0040), __byte_perm(rb[6], rb[7], 0x0040), 0x5410);
+        int8_t* run = xq + ((size_t)(v >> 2) << 5);
+        const int i = v & 3;
+        /* The two weight-GEMM layouts interleave the bytes of the four threads
+         * that share a run: the bytes are exchanged with shuffles so that every
+         * thread stores two whole 32-bit words instead of eight single bytes.
+         * (All four threads of a run are in range together: nvec % 4 == 0.) */
+        if (LAYOUT == 0) {
+            if (ok) *reinterpret_cast<uint2*>(run + (i << 3)) = make_uint2(lo, hi);
+        } else if (LAYOUT == 1) {
+            /* evens of the chunk at 4i.., odds at 16 + 4i.. */
+            if (ok) {
+                *reinterpret_cast<uint32_t*>(run + (i << 2)) = __byte_perm(lo, hi, 0x6420);
+                *reinterpret_cast<uint32_t*>(run + 16 + (i << 2)) = __byte_perm(lo, hi, 0x7531);
+            }
+        } else if (LAYOUT == 3) {
+            /* byte position 16*odd + 4*word + i: word w of the run's first half
+             * is column 2w of the four chunks, of its second half column 2w+1 */
+            const uint32_t w0 = transpose4(__byte_perm(lo, hi, 0x6420), t & 3);
+            const uint32_t w1 = transpose4(__byte_perm(lo, hi, 0x7531), t & 3);
+            if (ok) {
+                *reinterpret_cast<uint32_t*>(run + (i << 2)) = w0;
+                *reinterpret_cast<uint32_t*>(run + 16 + (i << 2)) = w1;
+            }
+        } else {
+            /* word 2w + (i & 1) = [chunk i&1: col 2w, chunk (i&1)+2: col 2w, then both again for
+             * col 2w+1]: threads i and i^2 swap halves and each builds two words */
+            const bool high = (t & 2) != 0;
+            const uint32_t x = __shfl_xor_sync(0xffffffffu, high ? lo : hi, 2);
+            const uint32_t first = high ? x : lo, second = high ? hi : x;
+            const int o0 = (high ? 16 : 0) + 4 * (t & 1);
+            if (ok) {
+                *reinterpret_cast<uint32_t*>(run + o0) = __byte_perm(first, second, 0x5140);
+                *reinterpret_cast<uint32_t*>(run + o0 + 8) = __byte_perm(first, second, 0x7362);
+            }
+        }
+        if (SUMS) {
+            int s = __dp4a((int)lo, 0x01010101, __dp4a((int)hi, 0x01010101, 0));   /* sum of the 8 signed bytes */
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            if (ok && (t & 3) == 0) xsum[v >> 2] = s;
+        }
+    }
+}
+
 /* MAXT: the largest CTA an instance is launched with; MINB: CTAs per SM it is
  * compiled for, i.e. a register budget of 65536 / (MAXT * MINB). These kernels
  * alternate loads, two CTA-wide reductions and a long arithmetic tail, and they
@@ -140,85 +218,26 @@ act_quant_kernel(const ActQuantArgs a) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
 
+    /* 3. quantize the vectors this thread holds: the layout and the presence of run
+     * sums are decided ONCE per thread here, not once per vector inside the loop (the
+     * per-vector tests were a tenth of the kernel's instructions). */
     const float inv = (amax > 0.0f) ? __fdiv_rn(127.0f, amax) : 0.0f;
     if (t == 0) a.sx[row] = __fdiv_rn(amax, 127.0f);
-
-    /* 3. quantize the vectors this thread holds. Vector v covers columns
-     * 8v..8v+7: chunk i = v & 3 of run v >> 2. Four consecutive threads hold
-     * the four chunks of a run (G is a multiple of 32), which is what the
-     * per-run sum needs. */
     int8_t* xq = a.xq + (size_t)row * (size_t)a.nvec * 8u;
     int32_t* xsum = a.xsum ? a.xsum + (size_t)row * (size_t)(a.nvec >> 2) : nullptr;
-    const float2 inv2 = splat2(inv);
-#pragma unroll
-    for (int j = 0; j < VPT; j++) {
-        const int v = t + j * G;
-        const bool ok = VVB_Q_IN(j);
-        /* round-half-even without the conversion unit: p = v*inv is rounded
-         * to float first (as the CPU does) and adding 1.5*2^23 rounds it to an
-         * integer in the float adder's nearest-even mode; the low byte of the
-         * sum's bit pattern is then q as a signed byte (the constant's low
-         * byte is zero). The reference's clamp to +-127 can never act: amax is
-         * the exact maximum of |v|, so |p| <= amax * fl(127/amax) <
-         * 127.00002 and rounds to at most 127. (Rows holding an infinity or
-         * a NaN have no defined quantization on the CPU path either.) */
-        uint32_t rb[8];
-        const uint32_t* yw = reinterpret_cast<const uint32_t*>(&yv[j]);
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            /* two columns per packed multiply; the adds stay scalar: the
-             * assembler merges a packed multiply and a packed add into one
-             * fused multiply-add even when both name .rn, which skips the
-             * rounding of the product and moves ties */
-            const float2 p = mul2(unpack2(yw[e]), inv2);
-            rb[2 * e] = __float_as_uint(__fadd_rn(p.x, 12582912.0f));
-            rb[2 * e + 1] = __float_as_uint(__fadd_rn(p.y, 12582912.0f));
+    if (xsum != nullptr) {
+        switch (a.layout) {
+            case 0: quantize_vectors<VPT, GUARD, 0, true>(yv, inv, t, G, a.nvec, xq, xsum); break;
+            case 1: quantize_vectors<VPT, GUARD, 1, true>(yv, inv, t, G, a.nvec, xq, xsum); break;
+            case 2: quantize_vectors<VPT, GUARD, 2, true>(yv, inv, t, G, a.nvec, xq, xsum); break;
+            default: quantize_vectors<VPT, GUARD, 3, true>(yv, inv, t, G, a.nvec, xq, xsum); break;
         }
-        const uint32_t lo = __byte_perm(__byte_perm(rb[0], rb[1], 0x0040), __byte_perm(rb[2], rb[3], 0x0040), 0x5410);
-        const uint32_t hi = __byte_perm(__byte_perm(rb[4], rb[5], 0x0040), __byte_perm(rb[6], rb[7], 0x0040), 0x5410);
-        int s = __dp4a((int)lo, 0x01010101, __dp4a((int)hi, 0x01010101, 0));   /* sum of the 8 signed bytes */
-        /* The two weight-GEMM layouts interleave the bytes of the four threads
-         * that share a run: the bytes are exchanged with shuffles so that every
-         * thread stores two whole 32-bit words instead of eight single bytes.
-         * (All four threads of a run are in range together: nvec % 4 == 0.) */
-        uint32_t w0 = 0, w1 = 0;
-        int o0 = 0;
-        if (a.layout == 3) {
-            /* byte position 16*odd + 4*word + i: word w of the run's first half
-             * is column 2w of the four chunks, of its second half column 2w+1 */
-            w0 = transpose4(__byte_perm(lo, hi, 0x6420), t & 3);
-            w1 = transpose4(__byte_perm(lo, hi, 0x7531), t & 3);
-        } else if (a.layout == 2) {
-            /* word 2w + (i & 1) = [chunk i&1: col 2w, chunk (i&1)+2: col 2w, then both again for
-             * col 2w+1]: threads i and i^2 swap halves and each builds two words */
-            const bool high = (t & 2) != 0;
-            const uint32_t x = __shfl_xor_sync(0xffffffffu, high ? lo : hi, 2);
-            const uint32_t first = high ? x : lo, second = high ? hi : x;
-            w0 = __byte_perm(first, second, 0x5140);
-            w1 = __byte_perm(first, second, 0x7362);
-            o0 = (high ? 16 : 0) + 4 * (t & 1);
-        }
-        if (ok) {
-            int8_t* run = xq + ((size_t)(v >> 2) << 5);
-            const int i = v & 3;
-            if (a.layout == 0) {
-                *reinterpret_cast<uint2*>(run + (i << 3)) = make_uint2(lo, hi);
-            } else if (a.layout == 1) {
-                /* evens of the chunk at 4i.., odds at 16 + 4i.. */
-                *reinterpret_cast<uint32_t*>(run + (i << 2)) = __byte_perm(lo, hi, 0x6420);
-                *reinterpret_cast<uint32_t*>(run + 16 + (i << 2)) = __byte_perm(lo, hi, 0x7531);
-            } else if (a.layout == 3) {
-                *reinterpret_cast<uint32_t*>(run + (i << 2)) = w0;
-                *reinterpret_cast<uint32_t*>(run + 16 + (i << 2)) = w1;
-            } else {
-                *reinterpret_cast<uint32_t*>(run + o0) = w0;
-                *reinterpret_cast<uint32_t*>(run + o0 + 8) = w1;
-            }
-        }
-        if (xsum != nullptr) {
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            if (ok && (t & 3) == 0) xsum[v >> 2] = s;
+    } else {
+        switch (a.layout) {
+            case 0: quantize_vectors<VPT, GUARD, 0, false>(yv, inv, t, G, a.nvec, xq, xsum); break;
+            case 1: quantize_vectors<VPT, GUARD, 1, false>(yv, inv, t, G, a.nvec, xq, xsum); break;
+            case 2: quantize_vectors<VPT, GUARD, 2, false>(yv, inv, t, G, a.nvec, xq, xsum); break;
+            default: quantize_vectors<VPT, GUARD, 3, false>(yv, inv, t, G, a.nvec, xq, xsum); break;
         }
     }
 }

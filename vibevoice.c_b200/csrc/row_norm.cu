@@ -67,6 +67,21 @@ row_norm_plain_kernel(const RowNormArgs a) {
     row_norm_body<VPT, 1, GUARD, true, 0>(a, blockIdx.x, threadIdx.x, blockDim.x, 0);
 }
 
+/* ... and when the row splits into whole vectors over 64 threads (hidden sizes
+ * 1536 .. 4096 in steps of 512) it runs as TWO WARPS PER ROW, 3 .. 8 vectors per
+ * thread, twelve such rows resident per SM: 32.8 us for [14449, 3584] (0.97 of
+ * the measured copy rate) against 35.5 for the instance above; compiled for 16
+ * CTAs per SM (64 registers) 35.0. The same shape WITH an addend is slower than
+ * 128 threads x 4 (64.6 against 62.7 us), so the add + norm keeps that. */
+constexpr int kTwoWarpThreads = 64;
+template <int VPT>
+__global__ void __launch_bounds__(kTwoWarpThreads, 12)
+row_norm_two_warp_kernel(const RowNormArgs a) {
+    pdl_wait();
+    pdl_trigger();
+    row_norm_body<VPT, 1, GUARD_NONE, true, 0>(a, blockIdx.x, threadIdx.x, kTwoWarpThreads, 0);
+}
+
 /* ----------------------------------------------------------------- generic */
 struct RowNormGenericArgs {
     const __half* src;
@@ -191,6 +206,23 @@ static void launch_cta_vpt(const RowNormArgs& a, int threads, cudaStream_t s) {
 }
 
 static cudaError_t launch_cta(const RowNormArgs& a, int vpt, int threads, cudaStream_t s) {
+    if (a.rows > kLatencyRows && a.ids == nullptr && a.delta == nullptr && a.nvec % kTwoWarpThreads == 0) {
+        const dim3 grid(a.rows), block(kTwoWarpThreads);
+        bool done = true;
+        switch (a.nvec / kTwoWarpThreads) {
+            case 3: launch_pdl(row_norm_two_warp_kernel<3>, grid, block, 0, s, a); break;
+            case 4: launch_pdl(row_norm_two_warp_kernel<4>, grid, block, 0, s, a); break;
+            case 5: launch_pdl(row_norm_two_warp_kernel<5>, grid, block, 0, s, a); break;
+            case 6: launch_pdl(row_norm_two_warp_kernel<6>, grid, block, 0, s, a); break;
+            case 7: launch_pdl(row_norm_two_warp_kernel<7>, grid, block, 0, s, a); break;
+            case 8: launch_pdl(row_norm_two_warp_kernel<8>, grid, block, 0, s, a); break;
+            default: done = false;
+        }
+        if (done) {
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            return cudaGetLastError();
+        }
+    }
     switch (vpt) {
         case 1: launch_pdl(row_norm_cta_kernel<1, GUARD_ALL, 1024, 2>, dim3(a.rows), dim3(threads), 0, s, a); break;
         case 2: launch_cta_vpt<2>(a, threads, s); break;
