@@ -185,18 +185,13 @@ __device__ __forceinline__ void row_norm_produce(const RowNormArgs& a, int row, 
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             if (has_delta) hw[e] = hadd2_bits(hw[e], dw[e]);
-#ifdef VVB_SS_DIRECT
-            /* half -> double in one conversion each, without the detour through float */
+            /* half -> double in ONE conversion each (exact either way; the detour
+             * through float cost an instruction per element: rmsnorm_q8 36.2 -> 35.1 us) */
             double dx, dy;
             asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f64.f16 %0, lo;\n\tcvt.f64.f16 %1, hi;\n\t}"
                 : "=d"(dx), "=d"(dy) : "r"(hw[e]));
             ss = fma(dx, dx, ss);
             ss1 = fma(dy, dy, ss1);
-#else
-            const float2 f = unpack2(hw[e]);
-            ss = fma((double)f.x, (double)f.x, ss);
-            ss1 = fma((double)f.y, (double)f.y, ss1);
-#endif
         }
     }
     if (a.row_out != nullptr) {

@@ -89,7 +89,9 @@ __host__ __device__ constexpr float tq_threshold(int j) {
 
 /* 128-point Walsh-Hadamard transform over a warp, four values per lane: strides
  * 1 and 2 inside the lane, strides 4 .. 64 against lane ^ 1 .. lane ^ 16; the
- * lane with the stride's bit set keeps (other - own), the other (own + other). */
+ * lane with the stride's bit set keeps (other - own), the other (own + other).
+ * Both are one fused multiply-add of the own value by -1 or +1 onto the other:
+ * the product is exact, so the single rounding is that of the addition. */
 __device__ __forceinline__ void tq_wht128(float (&v)[4], int lane) {
     float a;
     a = __fadd_rn(v[0], v[1]); v[1] = __fsub_rn(v[0], v[1]); v[0] = a;
@@ -98,11 +100,11 @@ __device__ __forceinline__ void tq_wht128(float (&v)[4], int lane) {
     a = __fadd_rn(v[1], v[3]); v[3] = __fsub_rn(v[1], v[3]); v[1] = a;
 #pragma unroll
     for (int m = 1; m < 32; m <<= 1) {
-        const bool upper = (lane & m) != 0;
+        const float own = (lane & m) ? -1.0f : 1.0f;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const float o = __shfl_xor_sync(0xffffffffu, v[i], m);
-            v[i] = upper ? __fsub_rn(o, v[i]) : __fadd_rn(v[i], o);
+            v[i] = __fmaf_rn(v[i], own, o);
         }
     }
 }
@@ -122,6 +124,21 @@ __device__ __forceinline__ float tq_div_approx(float x, float y) {
     asm("div.approx.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(x), "f"(y));
     return r;
 }
+
+/* The threshold to test at bit STEP of a code whose higher bits are known:
+ * threshold number BASE + 2^STEP - 1, BASE the value of the higher bits; a tree
+ * of selects on those bits (LEVEL walks from the top bit down to STEP + 1). */
+template <int FMT, int LEVEL, int STEP, int BASE>
+struct TqPivot {
+    static __device__ __forceinline__ float get(const bool (&hit)[4]) {
+        if constexpr (LEVEL <= STEP) {
+            return tq_threshold<FMT>(BASE + (1 << STEP) - 1);
+        } else {
+            return hit[LEVEL] ? TqPivot<FMT, LEVEL - 1, STEP, BASE + (1 << LEVEL)>::get(hit)
+                              : TqPivot<FMT, LEVEL - 1, STEP, BASE>::get(hit);
+        }
+    }
+};
 
 /* Codes of a lane's four values. */
 template <int FMT>
@@ -143,14 +160,25 @@ __device__ __forceinline__ uint32_t tq_pack4(const float (&y)[4], float inv_sigm
         }
         return bits;
     }
+    /* The code of a value is how many of the ascending thresholds it exceeds: a
+     * binary search over them, every pivot picked among immediates by the
+     * outcomes so far (15 compares and 15 adds become 4 compares and 11 selects
+     * for the 4-bit format). A NaN exceeds nothing: code 0, as by counting. */
     constexpr int W = (FMT == KV_TQ4) ? 4 : (FMT == KV_TQ3) ? 3 : 2;
-    constexpr int NLEV = 1 << W;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const float t = __fmul_rn(y[i], inv_sigma);
+        bool hit[4] = {false, false, false, false};      /* hit[s]: bit s of the code */
         uint32_t c = 0;
 #pragma unroll
-        for (int j = 0; j + 1 < NLEV; j++) c += (t > tq_threshold<FMT>(j)) ? 1u : 0u;
+        for (int step = W - 1; step >= 0; step--) {
+            const float pivot = step == 3 ? TqPivot<FMT, 3, 3, 0>::get(hit)
+                              : step == 2 ? TqPivot<FMT, W - 1, 2, 0>::get(hit)
+                              : step == 1 ? TqPivot<FMT, W - 1, 1, 0>::get(hit)
+                                          : TqPivot<FMT, W - 1, 0, 0>::get(hit);
+            hit[step] = t > pivot;
+            c |= hit[step] ? (1u << step) : 0u;
+        }
         bits |= c << (W * i);
     }
     return bits;
