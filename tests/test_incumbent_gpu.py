@@ -49,6 +49,8 @@ def libs():
     ref.vv_bias_add_dev.argtypes = [vp, vp, i, i, vp]
     if hasattr(ref, "vv_kv_quant_store_dev"):
         ref.vv_kv_quant_store_dev.argtypes = [vp, vp, vp, vp, vp, vp, vp, C.c_bool, i, i, i, vp, i, i, vp]
+    if hasattr(ref, "vv_kv_store_dev"):
+        ref.vv_kv_store_dev.argtypes = [vp, vp, vp, vp, vp, vp, vp, C.c_bool, i, i, i, vp, i, i, vp, vp]
     return vvb200, ref
 
 
@@ -213,6 +215,38 @@ def test_fp8_kv_append_vs_incumbent(libs):
                                          NKV, HD, 0, None, rows, 1, s) == 0
     theirs = time_graph(ref_seq, n)
     record(f"bias + rope + fp8 e4m3 kv store [{rows},28+4+4,128]", ours, theirs)
+
+
+def test_tq4_kv_append_vs_incumbent(libs):
+    """The same append into the 4-bit TurboQuant cache (64 bytes and one FP16 RMS per head
+    vector): one launch here; bias x3, RoPE x2 and vv_kv_store_dev in the reference."""
+    vv, ref = libs
+    if not hasattr(ref, "vv_kv_store_dev"):
+        pytest.skip("the reference's kv_quant.cu is not in the compiled library")
+    rows, fmt, bpv = 14449, vv.VVB_KV_TQ4, 64
+    n = nsets(rows * (2 * NQ + 2 * NKV) * HD * 2)
+    qs, ks, vs = ([rn(rows, h, HD) for _ in range(n)] for h in (NQ, NKV, NKV))
+    kst = [torch.empty(rows, NKV * bpv, device="cuda", dtype=torch.uint8) for _ in range(n)]
+    vst = [torch.empty(rows, NKV * bpv, device="cuda", dtype=torch.uint8) for _ in range(n)]
+    kmt = [torch.empty(rows, NKV, device="cuda", dtype=torch.float16) for _ in range(n)]
+    vmt = [torch.empty(rows, NKV, device="cuda", dtype=torch.float16) for _ in range(n)]
+    bq, bk, bv, kref = rn(NQ * HD), rn(NKV * HD), rn(NKV * HD), rn(NKV * HD)
+
+    def ours_fn(k, s):
+        assert vv.vvb_kv_append_dev(qs[k], ks[k], vs[k], kst[k], vst[k], rows, NQ, NKV, HD, q_bias=bq, k_bias=bk,
+                                    v_bias=bv, kv_format=fmt, k_ref=kref, k_meta=kmt[k], v_meta=vmt[k], stream=s) == 0
+    ours = time_graph(ours_fn, n)
+
+    def ref_seq(k, s):
+        assert ref.vv_bias_add_dev(p(qs[k]), p(bq), rows, NQ * HD, s) == 0
+        assert ref.vv_bias_add_dev(p(ks[k]), p(bk), rows, NKV * HD, s) == 0
+        assert ref.vv_bias_add_dev(p(vs[k]), p(bv), rows, NKV * HD, s) == 0
+        assert ref.vv_rope_dev(p(qs[k]), rows, NQ, HD, 0, None, 1e6, s) == 0
+        assert ref.vv_rope_dev(p(ks[k]), rows, NKV, HD, 0, None, 1e6, s) == 0
+        assert ref.vv_kv_store_dev(p(ks[k]), p(vs[k]), p(kst[k]), p(vst[k]), p(kmt[k]), p(vmt[k]), p(kref), False,
+                                   NKV, HD, 0, None, rows, fmt, None, s) == 0
+    theirs = time_graph(ref_seq, n)
+    record(f"bias + rope + 4-bit TurboQuant kv store [{rows},28+4+4,128]", ours, theirs)
 
 
 def test_lm_head_vs_incumbent(libs):

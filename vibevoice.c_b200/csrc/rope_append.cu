@@ -56,6 +56,7 @@ namespace vvb {
 extern std::atomic<uint64_t> g_launches;
 
 constexpr int kVRowsPerCta = 32;
+constexpr int kTqPair = 2;           /* TurboQuant: head vectors a warp works on side by side */
 
 /* CTAs per SM the FP16 variant is compiled for (the FP8 variants take 3: at 4
  * they spill and run 61.7 instead of 48.0 us; the FP16 variant measures 43.8 us
@@ -124,28 +125,44 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
             const int warp = t >> 5, lane = t & 31;
             const int nvecs = min(kVRowsPerCta, a.rows - row0v) * a.n_kv;
             const uint2* vsrc = reinterpret_cast<const uint2*>(A.v) + (size_t)row0v * a.n_kv * 32;
-            for (int base = warp; base < nvecs; base += (kRopeThreads / 32) * kU) {
+            /* (row, head) of vector idx = warp + 8 * n, kept by stepping instead of dividing */
+            constexpr int kWarps = kRopeThreads / 32;
+            const int step_r = kWarps / a.n_kv, step_h = kWarps - step_r * a.n_kv;
+            int rl = warp / a.n_kv, h = warp - rl * a.n_kv;
+            for (int base = warp; base < nvecs; base += kWarps * kU) {
                 uint2 x[kU];
 #pragma unroll
                 for (int j = 0; j < kU; j++) {
-                    const int idx = base + j * (kRopeThreads / 32);
+                    const int idx = base + j * kWarps;
                     if (idx < nvecs) x[j] = __ldcs(vsrc + (size_t)idx * 32 + lane);
                 }
 #pragma unroll
-                for (int j = 0; j < kU; j++) {
-                    const int idx = base + j * (kRopeThreads / 32);
-                    if (idx >= nvecs) continue;           /* warp-uniform */
-                    const int rl = idx / a.n_kv, h = idx - rl * a.n_kv;
-                    uint2 xv = x[j];
-                    if (A.v_bias) {
-                        const uint2 b = __ldg(reinterpret_cast<const uint2*>(A.v_bias) + h * 32 + lane);
-                        xv.x = hadd2_bits(xv.x, b.x);
-                        xv.y = hadd2_bits(xv.y, b.y);
+                for (int j0 = 0; j0 < kU; j0 += kTqPair) {
+                    float v4[kTqPair][4];
+                    uint8_t* dstp[kTqPair];
+                    __half* metap[kTqPair];
+                    bool livep[kTqPair];
+#pragma unroll
+                    for (int n = 0; n < kTqPair; n++) {
+                        const int idx = base + (j0 + n) * kWarps;
+                        livep[n] = idx < nvecs;               /* warp-uniform */
+                        uint2 xv = livep[n] ? x[j0 + n] : make_uint2(0u, 0u);
+                        if (A.v_bias && livep[n]) {
+                            const uint2 b = __ldg(reinterpret_cast<const uint2*>(A.v_bias) + h * 32 + lane);
+                            xv.x = hadd2_bits(xv.x, b.x);
+                            xv.y = hadd2_bits(xv.y, b.y);
+                        }
+                        const float2 f0 = unpack2(xv.x), f1 = unpack2(xv.y);
+                        v4[n][0] = f0.x; v4[n][1] = f0.y; v4[n][2] = f1.x; v4[n][3] = f1.y;
+                        const size_t at = livep[n]
+                            ? cache_row(PAGED ? A.page_table : nullptr, cache_first_v + row0v + rl) * a.n_kv + h : 0;
+                        dstp[n] = reinterpret_cast<uint8_t*>(A.v_cache) + at * BPV;
+                        metap[n] = A.v_meta + at;
+                        h += step_h;
+                        rl += step_r;
+                        if (h >= a.n_kv) { h -= a.n_kv; rl++; }
                     }
-                    const float2 f0 = unpack2(xv.x), f1 = unpack2(xv.y);
-                    float v4[4] = {f0.x, f0.y, f1.x, f1.y};
-                    const size_t at = cache_row(PAGED ? A.page_table : nullptr, cache_first_v + row0v + rl) * a.n_kv + h;
-                    tq_store_vec<FMT>(v4, lane, reinterpret_cast<uint8_t*>(A.v_cache) + at * BPV, A.v_meta + at);
+                    if (livep[0]) tq_store_vecs<FMT, kTqPair>(v4, lane, dstp, metap, livep);
                 }
             }
             return;
@@ -328,20 +345,36 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
             const int head0 = first_k_col / a.hvn - a.n_q;         /* first of them, as a KV head index */
             /* lane L's values 4L .. 4L+3: half (d >= 64), vector inside the half, first or second 8 bytes of it */
             const int half_sel = lane >> 4, vsel = (lane & 15) >> 1, part = lane & 1;
-            for (int idx = warp; idx < nrows * heads; idx += kRopeThreads / 32) {
-                const int rl = idx / heads, hk = idx - rl * heads;
-                const uint2 raw = reinterpret_cast<const uint2*>(&k_stage[(rl * 2 + half_sel) * kcols + hk * a.hvn + vsel])[part];
-                float2 f0 = unpack2(raw.x), f1 = unpack2(raw.y);
-                const int h = head0 + hk;
-                if (A.k_ref != nullptr) {
-                    const uint2 r = __ldg(reinterpret_cast<const uint2*>(A.k_ref) + h * 32 + lane);
-                    const float2 r0 = unpack2(r.x), r1 = unpack2(r.y);
-                    f0.x = __fsub_rn(f0.x, r0.x); f0.y = __fsub_rn(f0.y, r0.y);
-                    f1.x = __fsub_rn(f1.x, r1.x); f1.y = __fsub_rn(f1.y, r1.y);
+            constexpr int kWarps = kRopeThreads / 32;
+            const int step_r = kWarps / heads, step_h = kWarps - step_r * heads;
+            int rl = warp / heads, hk = warp - rl * heads;
+            for (int idx = warp; idx < nrows * heads; idx += kWarps * kTqPair) {
+                float v4[kTqPair][4];
+                uint8_t* dstp[kTqPair];
+                __half* metap[kTqPair];
+                bool livep[kTqPair];
+#pragma unroll
+                for (int n = 0; n < kTqPair; n++) {
+                    livep[n] = idx + n * kWarps < nrows * heads;      /* warp-uniform */
+                    const int rs = livep[n] ? rl : 0, hs = livep[n] ? hk : 0;
+                    const uint2 raw = reinterpret_cast<const uint2*>(&k_stage[(rs * 2 + half_sel) * kcols + hs * a.hvn + vsel])[part];
+                    float2 f0 = unpack2(raw.x), f1 = unpack2(raw.y);
+                    const int h = head0 + hs;
+                    if (A.k_ref != nullptr) {
+                        const uint2 r = __ldg(reinterpret_cast<const uint2*>(A.k_ref) + h * 32 + lane);
+                        const float2 r0 = unpack2(r.x), r1 = unpack2(r.y);
+                        f0.x = __fsub_rn(f0.x, r0.x); f0.y = __fsub_rn(f0.y, r0.y);
+                        f1.x = __fsub_rn(f1.x, r1.x); f1.y = __fsub_rn(f1.y, r1.y);
+                    }
+                    v4[n][0] = f0.x; v4[n][1] = f0.y; v4[n][2] = f1.x; v4[n][3] = f1.y;
+                    const size_t at = cache_row(PAGED ? A.page_table : nullptr, cache_first + row0 + rs) * a.n_kv + h;
+                    dstp[n] = reinterpret_cast<uint8_t*>(A.k_cache) + at * BPV;
+                    metap[n] = A.k_meta + at;
+                    hk += step_h;
+                    rl += step_r;
+                    if (hk >= heads) { hk -= heads; rl++; }
                 }
-                float v4[4] = {f0.x, f0.y, f1.x, f1.y};
-                const size_t at = cache_row(PAGED ? A.page_table : nullptr, cache_first + row0 + rl) * a.n_kv + h;
-                tq_store_vec<FMT>(v4, lane, reinterpret_cast<uint8_t*>(A.k_cache) + at * BPV, A.k_meta + at);
+                tq_store_vecs<FMT, kTqPair>(v4, lane, dstp, metap, livep);
             }
         }
     } else if (FMT != KV_RAW && staged) {

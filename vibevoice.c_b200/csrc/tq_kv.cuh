@@ -92,20 +92,28 @@ __host__ __device__ constexpr float tq_threshold(int j) {
  * lane with the stride's bit set keeps (other - own), the other (own + other).
  * Both are one fused multiply-add of the own value by -1 or +1 onto the other:
  * the product is exact, so the single rounding is that of the addition. */
-__device__ __forceinline__ void tq_wht128(float (&v)[4], int lane) {
-    float a;
-    a = __fadd_rn(v[0], v[1]); v[1] = __fsub_rn(v[0], v[1]); v[0] = a;
-    a = __fadd_rn(v[2], v[3]); v[3] = __fsub_rn(v[2], v[3]); v[2] = a;
-    a = __fadd_rn(v[0], v[2]); v[2] = __fsub_rn(v[0], v[2]); v[0] = a;
-    a = __fadd_rn(v[1], v[3]); v[3] = __fsub_rn(v[1], v[3]); v[1] = a;
+template <int NV>
+__device__ __forceinline__ void tq_wht128(float (&v)[NV][4], int lane) {
+#pragma unroll
+    for (int n = 0; n < NV; n++) {
+        float a;
+        a = __fadd_rn(v[n][0], v[n][1]); v[n][1] = __fsub_rn(v[n][0], v[n][1]); v[n][0] = a;
+        a = __fadd_rn(v[n][2], v[n][3]); v[n][3] = __fsub_rn(v[n][2], v[n][3]); v[n][2] = a;
+        a = __fadd_rn(v[n][0], v[n][2]); v[n][2] = __fsub_rn(v[n][0], v[n][2]); v[n][0] = a;
+        a = __fadd_rn(v[n][1], v[n][3]); v[n][3] = __fsub_rn(v[n][1], v[n][3]); v[n][1] = a;
+    }
 #pragma unroll
     for (int m = 1; m < 32; m <<= 1) {
         const float own = (lane & m) ? -1.0f : 1.0f;
+        float o[NV][4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float o = __shfl_xor_sync(0xffffffffu, v[i], m);
-            v[i] = __fmaf_rn(v[i], own, o);
-        }
+        for (int n = 0; n < NV; n++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) o[n][i] = __shfl_xor_sync(0xffffffffu, v[n][i], m);
+#pragma unroll
+        for (int n = 0; n < NV; n++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) v[n][i] = __fmaf_rn(v[n][i], own, o[n][i]);
     }
 }
 
@@ -184,46 +192,72 @@ __device__ __forceinline__ uint32_t tq_pack4(const float (&y)[4], float inv_sigm
     return bits;
 }
 
-/* One head vector, a warp: lane holds the four values x[4*lane ..] (already
- * minus the reference key). Writes bytes_per_vec bytes at `dst` (4-byte
- * aligned) and the FP16 sigma at `meta`. Every lane of the warp must call. */
-template <int FMT>
-__device__ __forceinline__ void tq_store_vec(float (&v)[4], int lane, uint8_t* dst, __half* meta) {
+/* NV head vectors, a warp, worked on side by side (the stages of one vector are a chain of
+ * shuffles; two or four chains in flight hide each other's latency): lane holds the four
+ * values x[4*lane ..] of each (already minus the reference key). Writes bytes_per_vec bytes
+ * at dst[n] (2-byte aligned) and the FP16 sigma at meta[n] for every n with live[n]
+ * (warp-uniform). Every lane of the warp must call. */
+template <int FMT, int NV>
+__device__ __forceinline__ void tq_store_vecs(float (&v)[NV][4], int lane, uint8_t* const (&dst)[NV],
+                                              __half* const (&meta)[NV], const bool (&live)[NV]) {
     constexpr int NB = TqBits<FMT>::N;
     const int d0 = lane * 4;
+    float sgn[4];
 #pragma unroll
-    for (int i = 0; i < 4; i++) v[i] = __fmul_rn(v[i], tq_sign(d0 + i));
-    tq_wht128(v, lane);
+    for (int i = 0; i < 4; i++) sgn[i] = tq_sign(d0 + i);
 #pragma unroll
-    for (int i = 0; i < 4; i++) v[i] = __fmul_rn(v[i], kTqWhtNorm);
-    float ss = 0.0f;
+    for (int n = 0; n < NV; n++)
 #pragma unroll
-    for (int i = 0; i < 4; i++) ss = __fmaf_rn(v[i], v[i], ss);
+        for (int i = 0; i < 4; i++) v[n][i] = __fmul_rn(v[n][i], sgn[i]);
+    tq_wht128<NV>(v, lane);
+    float ss[NV];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
-    /* sigma (stored) is the approximate square root of the mean square; the scale the codes
-     * are taken against is the approximate RECIPROCAL square root of that same mean -- what the
-     * reference's fast-math build makes of 1.0f / sigma -- not a reciprocal of sigma: the two
-     * differ in the last bit often enough to move a code once in some 10^4 vectors. */
-    const float mean_sq = fmaxf(tq_div_approx(ss, 128.0f), 1e-12f);
-    const float sigma = tq_sqrt_approx(mean_sq);
-    const uint32_t bits = tq_pack4<FMT>(v, tq_rsqrt_approx(mean_sq));
-
-    /* Word w of the vector holds bits [32w, 32w + 32): lanes floor(32w / NB) ..
-     * floor((32w + 31) / NB). Lane w (< words) gathers them with shuffles. */
-    constexpr int WORDS = NB;                         /* 32 lanes * NB bits / 32 */
-    constexpr int SPAN = (32 + NB - 1) / NB + 1;       /* lanes that can touch one word */
-    const int first = (32 * lane) / NB;                /* for lane = word index */
-    uint32_t word = 0;
+    for (int n = 0; n < NV; n++) {
+        ss[n] = 0.0f;
 #pragma unroll
-    for (int k = 0; k < SPAN; k++) {
-        const int src = first + k;
-        const uint32_t b = __shfl_sync(0xffffffffu, bits, src & 31);
-        const int shift = NB * src - 32 * lane;        /* where that lane's bits begin, relative to this word */
-        if (src < 32 && shift < 32) word |= (shift >= 0) ? (b << shift) : (b >> (-shift));
+        for (int i = 0; i < 4; i++) {
+            v[n][i] = __fmul_rn(v[n][i], kTqWhtNorm);
+            ss[n] = __fmaf_rn(v[n][i], v[n][i], ss[n]);
+        }
     }
-    if (lane < WORDS) reinterpret_cast<uint32_t*>(dst)[lane] = word;
-    if (lane == 0) *meta = __float2half_rn(sigma);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int n = 0; n < NV; n++) ss[n] = __fadd_rn(ss[n], __shfl_xor_sync(0xffffffffu, ss[n], o));
+#pragma unroll
+    for (int n = 0; n < NV; n++) {
+        /* sigma (stored) is the approximate square root of the mean square; the scale the codes
+         * are taken against is the approximate RECIPROCAL square root of that same mean -- what the
+         * reference's fast-math build makes of 1.0f / sigma -- not a reciprocal of sigma: the two
+         * differ in the last bit often enough to move a code once in some 10^4 vectors. */
+        const float mean_sq = fmaxf(tq_div_approx(ss[n], 128.0f), 1e-12f);
+        const float sigma = tq_sqrt_approx(mean_sq);
+        const uint32_t bits = tq_pack4<FMT>(v[n], tq_rsqrt_approx(mean_sq));
+
+        /* Lane L's NB bits are bits [NB * L, NB * (L + 1)) of the vector. 16 and 8 bits are a
+         * lane's own aligned store; 12 and 6 bits are put together over lane pairs / quads into
+         * three whole bytes, which the first lanes of the group store one byte each. The warp's
+         * stores cover one contiguous run of bytes_per_vec bytes. */
+        if constexpr (NB == 16) {
+            if (live[n]) reinterpret_cast<uint16_t*>(dst[n])[lane] = (uint16_t)bits;
+        } else if constexpr (NB == 8) {
+            if (live[n]) dst[n][lane] = (uint8_t)bits;
+        } else if constexpr (NB == 12) {
+            const uint32_t other = __shfl_xor_sync(0xffffffffu, bits, 1);
+            const uint32_t three = (lane & 1) ? (other | (bits << 12)) : (bits | (other << 12));
+            if (live[n]) {
+                uint8_t* at = dst[n] + 3 * (lane >> 1);
+                if (lane & 1) at[2] = (uint8_t)(three >> 16);
+                else { at[0] = (uint8_t)three; at[1] = (uint8_t)(three >> 8); }
+            }
+        } else {
+            uint32_t three = bits << (6 * (lane & 3));
+            three |= __shfl_xor_sync(0xffffffffu, three, 1);
+            three |= __shfl_xor_sync(0xffffffffu, three, 2);
+            if (live[n] && (lane & 3) != 3) dst[n][3 * (lane >> 2) + (lane & 3)] = (uint8_t)(three >> (8 * (lane & 3)));
+        }
+        if (live[n] && lane == 0) *meta[n] = __float2half_rn(sigma);
+    }
 }
 
 }  // namespace vvb
