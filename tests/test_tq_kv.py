@@ -256,6 +256,53 @@ def test_fused_append_writes_the_reference_kernels_bytes(vv, refk, orc, fmt, nam
 
 
 @gpu
+@pytest.mark.parametrize("fmt,name,bpv", FMTS)
+def test_extreme_and_nonfinite_vectors_match_the_reference_kernel(vv, refk, fmt, name, bpv):
+    """Vectors the code search must not trip over: infinities and NaNs (every scaled value is
+    then NaN and exceeds no threshold), values far outside the outermost threshold, the largest
+    halves, subnormals, exact zeros, and values on a grid of quarters. V goes through the fused
+    launch untouched (no bias), so both kernels see the same bits; codes and sigmas must be the
+    reference kernel's."""
+    rng = np.random.default_rng(40 + fmt)
+    rows = 96
+    v = (rng.standard_normal((rows, NKV, HD)) * 0.7).astype(np.float16)
+    v[1, 0, 17] = np.inf
+    v[2, 1, 5] = -np.inf
+    v[2, 1, 90] = np.inf
+    v[3, 2, :] = np.nan
+    v[4, 3, 64] = np.nan
+    v[5, 0, :] = 65504.0
+    v[6, 1, ::2] = 65504.0
+    v[6, 1, 1::2] = -65504.0
+    v[7, 2, :] = 6e-8                      # subnormal halves
+    v[8, 3, :] = 0
+    v[9, 0, :] = 0
+    v[9, 0, 3] = 1.0                       # one spike: every transformed value has the same size
+    v[10, 1, :] = (rng.integers(-16, 17, HD) * 0.25).astype(np.float16)
+    v[11, 2, :] = 1.0
+    v[12, 3, 7] = 1000.0                   # one value many sigmas out
+    q = rng.standard_normal((rows, NQ, HD)).astype(np.float16)
+    k = rng.standard_normal((rows, NKV, HD)).astype(np.float16)
+    dq, dk, dv = dev(q), dev(k), dev(v)
+    fill = lambda w, dt=torch.uint8: torch.full((rows, w), 0xA5 if dt == torch.uint8 else 7.0, dtype=dt, device="cuda")
+    ks, vs, km, vm = fill(NKV * bpv), fill(NKV * bpv), fill(NKV, torch.float16), fill(NKV, torch.float16)
+    assert vv.vvb_kv_append_dev(dq, dk, dv, ks, vs, rows, NQ, NKV, HD, kv_format=fmt, keep_k=1, k_meta=km,
+                                v_meta=vm) == 0
+    rks, rvs, rkm, rvm = fill(NKV * bpv), fill(NKV * bpv), fill(NKV, torch.float16), fill(NKV, torch.float16)
+    assert refk.vv_kv_store_dev(p(dk), p(dv), p(rks), p(rvs), p(rkm), p(rvm), None, False, NKV, HD, 0, None, rows, fmt,
+                                None, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(vs, rvs), "V codes"
+    assert torch.equal(ks, rks), "K codes"
+    # sigmas as bit patterns; a NaN sigma may differ in payload only
+    for got, want, what in ((vm, rvm, "V sigma"), (km, rkm, "K sigma")):
+        g, w = got.view(torch.int16).cpu().numpy(), want.view(torch.int16).cpu().numpy()
+        nan_g, nan_w = np.isnan(got.cpu().numpy()), np.isnan(want.cpu().numpy())
+        assert np.array_equal(nan_g, nan_w), what
+        assert np.array_equal(g[~nan_g], w[~nan_w]), what
+
+
+@gpu
 def test_tq_argument_checks(vv):
     x = torch.zeros(4, 4, 128, dtype=torch.float16, device="cuda")
     q = torch.zeros(4, 28, 128, dtype=torch.float16, device="cuda")

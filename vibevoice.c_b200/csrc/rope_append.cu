@@ -104,6 +104,8 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
     const int t = threadIdx.x;
     pdl_wait();
     pdl_trigger();
+    __shared__ TqCells tq_cells[1];
+    if constexpr (TqUsesCells<FMT>::value) tq_cells_fill<FMT>(tq_cells[0], t);
 
     /* The FIRST grid row (blockIdx.y == 0) carries V: no rotation, so no table
      * and no barrier -- a flat copy (+ bias, + FP8 encoding) of kVRowsPerCta
@@ -124,6 +126,7 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
             constexpr int kU = 4;
             const int warp = t >> 5, lane = t & 31;
             const int nvecs = min(kVRowsPerCta, a.rows - row0v) * a.n_kv;
+            if constexpr (TqUsesCells<FMT>::value) __syncthreads();       /* the cell table */
             const uint2* vsrc = reinterpret_cast<const uint2*>(A.v) + (size_t)row0v * a.n_kv * 32;
             /* (row, head) of vector idx = warp + 8 * n, kept by stepping instead of dividing */
             constexpr int kWarps = kRopeThreads / 32;
@@ -162,7 +165,7 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
                         rl += step_r;
                         if (h >= a.n_kv) { h -= a.n_kv; rl++; }
                     }
-                    if (livep[0]) tq_store_vecs<FMT, kTqPair>(v4, lane, dstp, metap, livep);
+                    if (livep[0]) tq_store_vecs<FMT, kTqPair>(v4, lane, dstp, metap, livep, tq_cells);
                 }
             }
             return;
@@ -374,7 +377,7 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
                     rl += step_r;
                     if (hk >= heads) { hk -= heads; rl++; }
                 }
-                tq_store_vecs<FMT, kTqPair>(v4, lane, dstp, metap, livep);
+                tq_store_vecs<FMT, kTqPair>(v4, lane, dstp, metap, livep, tq_cells);
             }
         }
     } else if (FMT != KV_RAW && staged) {
