@@ -421,14 +421,56 @@ def separate_ops(torch, vv, tensors, rows, first, stream, reduce, barrier):
     return out
 
 
+class numa_local:
+    """While inside: this thread runs on the CPUs of the NUMA node the GPU hangs off, so the pages
+    of host buffers allocated AND first touched inside land in that node's memory (Linux places a
+    page on the node of the thread that first touches it). The affinity is put back on exit. A box
+    that does not say where the GPU sits (no sysfs entry, node -1, one node) is left alone."""
+
+    def __init__(self, torch, local):
+        self.info = {"gpu_numa_node": None, "bound": False}
+        self.saved = None
+        self.cpus = set()
+        try:
+            pr = torch.cuda.get_device_properties(local)
+            bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+            node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
+            self.info["gpu_numa_node"] = node
+            if node >= 0:
+                cpus = set()
+                for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+                    lo, _, hi = part.partition("-")
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+                self.cpus = cpus & os.sched_getaffinity(0)
+            else:
+                self.cpus = set()
+        except Exception:            # no such device property, no sysfs entry, an unreadable list
+            self.cpus = set()
+
+    def __enter__(self):
+        if self.cpus and self.cpus != os.sched_getaffinity(0):
+            self.saved = os.sched_getaffinity(0)
+            os.sched_setaffinity(0, self.cpus)
+            self.info["bound"] = True
+            self.info["cpus_on_node"] = len(self.cpus)
+        return self
+
+    def __exit__(self, *exc):
+        if self.saved is not None:
+            os.sched_setaffinity(0, self.saved)
+        return False
+
+
+
 def copy_ceiling(torch, local, h2d_bytes, d2h_bytes, barrier, reduce, rounds=3):
     """What the box's host<->device path gives this rank while every rank does
     the same: plain cudaMemcpyAsync of the step's byte counts from and to pinned
     memory, uploads on one stream and downloads on another, no kernels. The
     copies go in 64 MiB pieces (one call per piece)."""
     piece = 64 << 20
-    hb = torch.empty(piece, dtype=torch.uint8).pin_memory()
-    hb2 = torch.empty(piece, dtype=torch.uint8).pin_memory()
+    with numa_local(torch, local):
+        hb = torch.zeros(piece, dtype=torch.uint8).pin_memory()
+        hb2 = torch.zeros(piece, dtype=torch.uint8).pin_memory()
     db = torch.empty(piece, dtype=torch.uint8, device="cuda")
     db2 = torch.empty(piece, dtype=torch.uint8, device="cuda")
     s_up, s_down = torch.cuda.Stream(), torch.cuda.Stream()
@@ -464,8 +506,9 @@ def copy_ceiling(torch, local, h2d_bytes, d2h_bytes, barrier, reduce, rounds=3):
 def run_e2e(args, vv, torch, tensors, rows, first, local, total_rows, barrier, reduce):
     h0, d, w, q, k, g0, up = tensors
     pin = lambda t: t.cpu().pin_memory()
-    hh, hd_, hw, hq, hk, hg, hu = (pin(t) for t in (h0, d, w, q, k, g0, up))
-    hn = torch.empty_like(hh).pin_memory()
+    with numa_local(torch, local) as numa:
+        hh, hd_, hw, hq, hk, hg, hu = (pin(t) for t in (h0, d, w, q, k, g0, up))
+        hn = torch.zeros_like(hh).pin_memory()
     pipe = vv.HostPipeline(local, args.slice_rows, H, NQ, NKV, HD, INTER)
     hchain = vv.make_chain(hh, hd_, hw, hn, hq, hk, hg, hu, rows, H, NQ, NKV, HD, INTER, first, EPS, THETA)
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
@@ -495,6 +538,9 @@ def run_e2e(args, vv, torch, tensors, rows, first, local, total_rows, barrier, r
                         "what": "every rank copying its step's bytes host->device and device->host at once with "
                                 "plain cudaMemcpyAsync from/to pinned memory, no kernels"},
             "frac_of_ceiling": ceiling_ms / ms,
+            "host_buffers": {"pinned": True, "numa": numa.info,
+                             "what": "allocated and first touched on the CPUs of the GPU's NUMA node when the box "
+                                     "names one"},
             "api": "vvb_layer_chain_host (pinned host tensors; uploads, kernels and downloads pipelined in "
                    f"{args.slice_rows}-row slices)"}
 
