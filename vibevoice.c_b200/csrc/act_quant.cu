@@ -44,7 +44,9 @@ enum { Q_PLAIN = 0, Q_RMSNORM = 1, Q_SWIGLU = 2 };
  * layout), act_quant 22.3 against 26.3; 224 threads x 2 vectors, the other
  * padding-free shape, is slower than both (55 us). */
 constexpr int kTwoWarpThreads = 64;
-constexpr int kTwoWarpMinB = 12;          /* CTAs per SM: 80 registers per thread */
+/* CTAs per SM of the two-warp shape. Measured on rmsnorm_q8 [14449, 3584]: 12 (80 registers)
+ * 35.1 us; 14 (72 registers, three spilled words) 33.9; 16 (64 registers, 22 spilled words) 35.2. */
+constexpr int kTwoWarpMinB = 14;
 static inline int two_warp_vpt(int rows, int nvec, int mode) {
     if (mode == 2 || rows <= kLatencyRows || nvec % kTwoWarpThreads != 0) return 0;
     const int v = nvec / kTwoWarpThreads;
