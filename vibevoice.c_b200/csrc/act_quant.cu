@@ -63,14 +63,14 @@ struct ActQuantArgs {
     int rows, nvec, layout;
 };
 
-/* Column j (0..31) of a run -> byte position (include/vibevoice/q8.h:64-73). */
-__device__ __forceinline__ int q8_pos(int layout, int j) {
-    const int odd = j & 1, word = (j >> 1) & 3, slot = (j >> 3) + 4 * odd;
-    if (layout == 1) return odd ? 16 + (j >> 1) : (j >> 1);
-    if (layout == 2) return 8 * word + 4 * (slot & 1) + (slot >> 1);
-    if (layout == 3) return 16 * odd + 4 * word + (slot & 3);
-    return j;
-}
+/* Byte position of column j (0..31) of a run in the four layouts
+ * (include/vibevoice/q8.h:64-73), with odd = j & 1, word = (j >> 1) & 3,
+ * slot = (j >> 3) + 4 * odd:
+ *   0 natural:  j
+ *   1:          odd ? 16 + (j >> 1) : (j >> 1)
+ *   2:          8 * word + 4 * (slot & 1) + (slot >> 1)
+ *   3 w4_mma:   16 * odd + 4 * word + (slot & 3)
+ * quantize_vectors below builds whole 32-bit words of these orders. */
 
 /* 4 x 4 byte transpose across four consecutive lanes: lane i (0..3) gives the
  * word [v_i.b0 .. v_i.b3] and receives [v_0.b_i, v_1.b_i, v_2.b_i, v_3.b_i].
