@@ -48,6 +48,7 @@ vv_status_t vvb_shard_rows(int64_t total_rows, int parts, int part,
 /* --------------------------------------------------------------- pipeline */
 
 #define VVB_SLOTS 3
+#define VVB_TAIL_MIN_ROWS 128      /* the tapering of the last slices stops here */
 
 typedef struct vvb_slot {
     void *hidden, *delta, *normed, *q, *k, *gate, *up;
@@ -184,9 +185,15 @@ vv_status_t vvb_layer_chain_host(vvb_host_ctx_t* c, const vvb_layer_chain_t* h) 
     CK(cudaMemcpyAsync(c->norm_w, h->norm_w, hrow, cudaMemcpyHostToDevice, c->s_up));
     c->last_h2d += hrow;
 
+    /* Slices are max_rows long until the last max_rows of the prompt, which go in halves
+     * (1024 -> 512, 256, 128, 128): the upload stream is the busy one, and what follows its last
+     * copy -- the last slice's kernels and download -- overlaps nothing, so that slice is
+     * kept short. */
     int slice = 0;
-    for (int r0 = 0; r0 < h->rows; r0 += c->max_rows, slice++) {
-        const int n = h->rows - r0 < c->max_rows ? h->rows - r0 : c->max_rows;
+    for (int r0 = 0, n = 0; r0 < h->rows; r0 += n, slice++) {
+        const int left = h->rows - r0;
+        n = left < c->max_rows ? left : c->max_rows;
+        if (left <= c->max_rows && left > VVB_TAIL_MIN_ROWS) n = (left + 1) / 2;
         vvb_slot_t* s = &c->slot[slice % VVB_SLOTS];
         const size_t off = (size_t)r0;
 
