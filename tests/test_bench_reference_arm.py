@@ -36,3 +36,30 @@ def test_reference_arm_ignores_the_launchers_omp_setting():
 def test_reference_arm_other_ranks_do_nothing():
     r = run_arm(1, 2)
     assert r.returncode == 0 and r.stdout.strip() == ""
+
+
+def test_numa_placement_scope_restores_the_affinity(tmp_path, monkeypatch):
+    """bench.py places its pinned host buffers on the GPU's NUMA node by narrowing the thread's CPU
+    affinity while it allocates them; a box that names no node is left alone, and the affinity is
+    back to what it was on leaving the scope either way."""
+    sys.path.insert(0, ROOT)
+    import importlib
+    bench = importlib.import_module("bench")
+    before = os.sched_getaffinity(0)
+
+    class NoGpu:                           # torch.cuda.get_device_properties raises without a device
+        class cuda:
+            @staticmethod
+            def get_device_properties(_):
+                raise RuntimeError("no CUDA device")
+    with bench.numa_local(NoGpu, 0) as scope:
+        assert scope.info == {"gpu_numa_node": None, "bound": False}
+        assert os.sched_getaffinity(0) == before
+    assert os.sched_getaffinity(0) == before
+
+    # a scope that does narrow the affinity (to one of the CPUs this process may use) undoes it
+    scope = bench.numa_local(NoGpu, 0)
+    scope.cpus = {min(before)}
+    with scope:
+        assert os.sched_getaffinity(0) == ({min(before)} if len(before) > 1 else before)
+    assert os.sched_getaffinity(0) == before
