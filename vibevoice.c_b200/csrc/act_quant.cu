@@ -43,10 +43,6 @@ enum { Q_PLAIN = 0, Q_RMSNORM = 1, Q_SWIGLU = 2 };
  * 40.3 us against 49.1 us for 128 x 4 (45.2 against 52.0 in the weight-GEMM
  * layout), act_quant 22.3 against 26.3; 224 threads x 2 vectors, the other
  * padding-free shape, is slower than both (55 us). */
-#ifndef VVB_SWIGLU_Q8_LOOKAHEAD
-#define VVB_SWIGLU_Q8_LOOKAHEAD 0
-#endif
-constexpr int kSwigluLookAheadRows = VVB_SWIGLU_Q8_LOOKAHEAD;
 constexpr int kTwoWarpThreads = 64;
 /* CTAs per SM of the two-warp shape. Measured on rmsnorm_q8 [14449, 3584]: 12 (80 registers)
  * 35.1 us; 14 (72 registers, three spilled words) 33.9; 16 (64 registers, 22 spilled words) 35.2. */
@@ -192,19 +188,6 @@ act_quant_kernel(const ActQuantArgs a) {
         vec16 bv[VPT];
         const vec16* ap = a.a + roff + t;
         const vec16* bp = a.b + roff + t;
-        if (MODE == Q_SWIGLU && kSwigluLookAheadRows > 0 && row + kSwigluLookAheadRows < a.rows) {
-            /* L2 look-ahead: this CTA asks for the rows a CTA about a wave later will load
-             * (128-byte lines: 8 vectors each; gate lines by the first threads, up lines by
-             * the next). The SwiGLU producer waits for DRAM (ncu: 7.8 long-scoreboard stalls
-             * per issue): its CTAs are large, few fit on an SM, and while they compute none of
-             * them has loads in flight. */
-            const int lines = (a.nvec + 7) >> 3;
-            const size_t far = (size_t)(row + kSwigluLookAheadRows) * (size_t)a.nvec;
-            for (int l = t; l < 2 * lines; l += G) {
-                const vec16* p = (l < lines ? a.a : a.b) + far + (size_t)((l < lines ? l : l - lines) << 3);
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
-            }
-        }
 #pragma unroll
         for (int j = 0; j < VPT; j++) {
             yv[j] = VVB_Q_IN(j) ? ld_stream(ap + j * G) : make_uint4(0, 0, 0, 0);
