@@ -289,10 +289,13 @@ def run_native(args):
     def launch_chain(on_stream):
         vv.check(vv.vvb_layer_chain_dev(chain, on_stream), "vvb_layer_chain_dev")
 
-    # One step = the chain's launches. They are captured once into a CUDA graph
-    # and replayed, so a step costs one graph launch on the host however short
-    # the kernels are (shards at 8 GPUs run ~45 us a step).
-    graph, nodes_per_step = None, 0
+    # One step = the chain's launches. A timed pass is K steps; the K steps are captured once
+    # into ONE CUDA graph and a pass replays it: the kernels of consecutive steps then follow
+    # each other as they do inside an engine's captured layer sequence (programmatic edges, the
+    # next kernel scheduled while this one drains), not a host-side graph launch apart -- which
+    # costs some 3 us a step and is a tenth of a 45 us step when the prompt is sharded over eight.
+    K = args.steps
+    graph, nodes_per_pass = None, 0
     if not args.no_graph:
         side = torch.cuda.Stream()
         side.wait_stream(stream)
@@ -302,15 +305,18 @@ def run_native(args):
             graph = torch.cuda.CUDAGraph()
             n0 = vv.launch_count()
             with torch.cuda.graph(graph, stream=side):
-                launch_chain(side)
-            nodes_per_step = vv.launch_count() - n0
+                for _ in range(K):
+                    launch_chain(side)
+            nodes_per_pass = vv.launch_count() - n0
         stream.wait_stream(side)
 
-    def step():
+    def run_pass():
+        """Exactly K steps."""
         if graph is not None:
             graph.replay()
         else:
-            launch_chain(stream)
+            for _ in range(K):
+                launch_chain(stream)
 
     sampler = None
     if rank == 0:
@@ -322,15 +328,15 @@ def run_native(args):
         sampler = ClockSampler(uuid, local)
         sampler.start()
 
-    K = args.steps
     warm = max(args.warmup, 3)
+    warm_passes = -(-warm // K)                  # warm-up runs whole passes: at least `warm` steps
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
-    for _ in range(warm):
-        step()
+    for _ in range(warm_passes):
+        run_pass()
     e1.record(stream)
     torch.cuda.synchronize()
-    est_ms = max(reduce([e0.elapsed_time(e1) / warm], "max")[0], 1e-3)
+    est_ms = max(reduce([e0.elapsed_time(e1) / (warm_passes * K)], "max")[0], 1e-3)
     repeats = args.repeats or min(2000, max(MIN_REPEATS, int(MIN_REGION_S * 1e3 / (K * est_ms)) + 1))
 
     # ---- timed passes: EXACTLY K steps under one CUDA-event pair, a barrier and a
@@ -344,14 +350,13 @@ def run_native(args):
         torch.cuda.synchronize()
         barrier()
         e0.record(stream)
-        for _ in range(K):
-            step()
+        run_pass()
         e1.record(stream)
         torch.cuda.synchronize()
         barrier()
         pass_ms.append(e0.elapsed_time(e1))
     t_region1 = time.perf_counter()
-    launches = (vv.launch_count() - launches0) if graph is None else nodes_per_step * K * repeats
+    launches = (vv.launch_count() - launches0) if graph is None else nodes_per_pass * repeats
     pass_ms = reduce(pass_ms, "max")
     launches_all = int(reduce([float(launches)], "sum")[0])
 
@@ -361,8 +366,8 @@ def run_native(args):
     torch.cuda.synchronize()
     barrier()
     t0 = time.perf_counter()
-    for _ in range(repeats * K):
-        step()
+    for _ in range(repeats):
+        run_pass()
     torch.cuda.synchronize()
     barrier()
     span_s = reduce([time.perf_counter() - t0], "max")[0]
@@ -602,7 +607,7 @@ def emit(args, world, total_rows, pass_ms, span_s, repeats, per, launches_all, c
         "chain_ops_separately": ops,
         "e2e": e2e_line,
         "gpu_launches": launches_all,
-        "launch_mode": ("direct" if args.no_graph else "one CUDA graph replay per step") +
+        "launch_mode": ("direct" if args.no_graph else "one CUDA graph replay per timed pass of K steps") +
                        f" ({launches_all // max(1, K * repeats * world)} kernel launch(es) per step per GPU: the chain's "
                        "three operations share one grid); gpu_launches counts all timed repeats",
         "clocks": clocks,
