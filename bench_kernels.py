@@ -220,8 +220,9 @@ def run(peak_gbs: float, peak_kind: str, only=None, plain=False):
                                                           HD, 0, 0, None, 1e6, vv.VVB_KV_FP8_E4M3, 0, s)),
            rows * (NQ + 2 * NKV) * HD * 2 + rows * 2 * NKV * HD,
            rows * (2 * NQ + 2 * NKV) * HD * 2 + rows * 2 * NKV * HD)
-    # and for the TurboQuant caches (4-bit and 1.5-bit): codes + one FP16 RMS per head vector
-    for fmt, fname, bpv in ((vv.VVB_KV_TQ4, "tq4", 64), (vv.VVB_KV_TQ1_5, "tq1_5", 24)):
+    # and for the four TurboQuant caches: codes + one FP16 RMS per head vector
+    for fmt, fname, bpv in ((vv.VVB_KV_TQ4, "tq4", 64), (vv.VVB_KV_TQ3, "tq3", 48), (vv.VVB_KV_TQ2, "tq2", 32),
+                            (vv.VVB_KV_TQ1_5, "tq1_5", 24)):
         R.case(f"rope_qk_append_{fname} [14449,28+4+4,128] with biases, reference key", None,
                lambda: (rn(rows, NQ, HD), rn(rows, NKV, HD), rn(rows, NKV, HD), u8(rows, NKV * bpv), u8(rows, NKV * bpv),
                         f16(rows, NKV), f16(rows, NKV)),
