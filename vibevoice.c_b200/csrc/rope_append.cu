@@ -6,7 +6,7 @@
  * (src/inference/decoder.c:463-464 vv_bias_add_dev on q, k, v; :850-855
  * vv_rope_dev on Q then K; src/inference/kv_cache.c:229-246 two device copies
  * of K and V into the layer's cache). Here one grid carries RoPE tiles
- * (rope.cuh) over the Q and K columns and, in its first grid row, flat copy CTAs
+ * (rope.cuh) over the Q and K columns and, as its first CTAs, flat copy CTAs
  * for V:
  *   Q head   x = f16(q + bias_q), rotate, store in place
  *   K head   x = f16(k + bias_k), rotate, store INTO THE CACHE row
@@ -79,6 +79,8 @@ struct RopeAppendArgs {
     const int* page_table;    /* may be null: logical position t lives in cache row t */
     int cache_offset;         /* cache row of row 0 (when r.d_position is null) */
     int keep_k;               /* also write the rotated K back in place */
+    int v_ctas;               /* the grid's first v_ctas CTAs carry V, the rest are RoPE tiles ... */
+    int row_tiles;            /* ... numbered row tile first: tile = chunk * row_tiles + row_tile */
 };
 
 /* Cache row of logical position t. A paged cache (the server's slots share one
@@ -107,14 +109,13 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
     __shared__ TqCells tq_cells[1];
     if constexpr (TqUsesCells<FMT>::value) tq_cells_fill<FMT>(tq_cells[0], t);
 
-    /* The FIRST grid row (blockIdx.y == 0) carries V: no rotation, so no table
+    /* The FIRST CTAs of the grid (blockIdx.x < v_ctas) carry V: no rotation, so no table
      * and no barrier -- a flat copy (+ bias, + FP8 encoding) of kVRowsPerCta
-     * rows per CTA into the cache. Fewer CTAs are needed than the grid has
-     * columns; the rest exit. These CTAs are the longest of the grid (each
+     * rows per CTA into the cache. These CTAs are the longest of the grid (each
      * walks 32 rows), so they are dispatched first and the short RoPE tiles
      * fill in behind them instead of waiting for a tail of V copies; four
      * loads per thread are in flight at a time. */
-    if (blockIdx.y == 0) {
+    if ((int)blockIdx.x < A.v_ctas) {
         const int cols_v = a.n_kv * 2 * a.hvn;                 /* vectors per V row */
         const int row0v = blockIdx.x * kVRowsPerCta;
         if (row0v >= a.rows) return;
@@ -193,10 +194,12 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
         }
         return;
     }
-    const int by = (int)blockIdx.y - 1;                        /* column chunk of this RoPE tile */
+    const int tile = (int)blockIdx.x - A.v_ctas;
+    const int by = (tile < A.row_tiles) ? 0 : tile / A.row_tiles;   /* column chunk of this RoPE tile */
+    const int bx = tile - by * A.row_tiles;                    /* its block of rows */
 
     const int rows_per_cta = a.row_slots * a.passes;
-    const int row0 = blockIdx.x * rows_per_cta;
+    const int row0 = bx * rows_per_cta;
     const int nrows = min(rows_per_cta, a.rows - row0);
 
     /* This thread's column (tensor, head, vector), fixed for all its rows. */
@@ -428,7 +431,7 @@ extern "C" int vvbk_rope_append(void* q, void* k, const void* v,
         return (int)cudaErrorNotSupported;
     RopeAppendArgs A;
     unsigned gx, gy;
-    /* tiles over the Q and K heads; one more grid row (the first) carries V */
+    /* a flat grid: the V CTAs first, then the tiles over the Q and K heads */
     /* TurboQuant: the CTA's rotated K tile (its K columns x 2 halves x its rows) must fit the
      * 512-vector staging buffer, which bounds the rows a CTA takes */
     int max_passes = kRopeMaxRowsPerThread;
@@ -441,8 +444,10 @@ extern "C" int vvbk_rope_append(void* q, void* k, const void* v,
     rope_plan(A.r, q, k, rows, n_q_heads, n_kv_heads, head_dim, position_offset, d_position, inv_freq,
               max_passes, &gx, &gy);
     const unsigned gx_v = (unsigned)((rows + kVRowsPerCta - 1) / kVRowsPerCta);
-    if (gx_v > gx) gx = gx_v;
-    gy += 1;
+    A.v_ctas = (int)gx_v;
+    A.row_tiles = (int)gx;
+    const unsigned long long total = (unsigned long long)gx * gy + gx_v;
+    if (total > 0x7fffffffull) return (int)cudaErrorInvalidValue;
     A.v = (const vec16*)v;
     A.k_cache = (vec16*)k_cache;
     A.v_cache = (vec16*)v_cache;
@@ -455,8 +460,7 @@ extern "C" int vvbk_rope_append(void* q, void* k, const void* v,
     A.page_table = page_table;
     A.cache_offset = cache_offset;
     A.keep_k = keep_k;
-    if (gy > 65535u) return (int)cudaErrorInvalidValue;
-    const dim3 grid(gx, gy), block(kRopeThreads);
+    const dim3 grid((unsigned)total), block(kRopeThreads);
     cudaStream_t s = (cudaStream_t)stream;
     /* the paged mapping is a template parameter so that the contiguous cache pays nothing for it */
 #define VVB_APPEND_CASE(F)                                                                          \
