@@ -41,6 +41,8 @@ def bias_add_f16(x, b):
     (48, 2, 1, 128, 5, 5, True, 0),             # the reference's tiny test model
     (17, 12, 2, 128, 100, 40, True, 0),         # BitNet-1.5B heads; cache row != position
     (9, 3, 3, 64, 7, 0, True, 1),
+    (70, 40, 8, 128, 33, 33, True, 1),          # 384 columns: two column chunks, K in the second
+    (37, 16, 2, 256, 3, 9, True, 0),            # head_dim 256: 288 columns, K split over both chunks' ends
 ])
 def test_rope_append_matches_oracle_and_separate_ops(vv, orc, rows, nq, nkv, hd, pos, cache_off, with_bias, keep_k):
     rng = np.random.default_rng(rows * 31 + nq)
