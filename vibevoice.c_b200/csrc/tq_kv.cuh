@@ -223,27 +223,27 @@ __device__ __forceinline__ uint32_t tq_pack4(const float (&y)[4], float inv_sigm
             const uint32_t c = (uint32_t)cells->below[cell] + ((t > cells->inside[cell]) ? 1u : 0u);
             bits |= c << (W * i);
         }
-        return bits;
-    }
-    /* The code of a value is how many of the ascending thresholds it exceeds: a
-     * binary search over them, every pivot picked among immediates by the
-     * outcomes so far (the 2- and 3-bit formats; the 4-bit one takes the cell table).
-     * A NaN exceeds nothing: code 0, as by counting. */
+    } else {
+        /* The code of a value is how many of the ascending thresholds it exceeds: a
+         * binary search over them, every pivot picked among immediates by the
+         * outcomes so far (the 2- and 3-bit formats; the 4-bit one takes the cell table).
+         * A NaN exceeds nothing: code 0, as by counting. */
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const float t = __fmul_rn(y[i], inv_sigma);
-        bool hit[4] = {false, false, false, false};      /* hit[s]: bit s of the code */
-        uint32_t c = 0;
+        for (int i = 0; i < 4; i++) {
+            const float t = __fmul_rn(y[i], inv_sigma);
+            bool hit[4] = {false, false, false, false};      /* hit[s]: bit s of the code */
+            uint32_t c = 0;
 #pragma unroll
-        for (int step = W - 1; step >= 0; step--) {
-            const float pivot = step == 3 ? TqPivot<FMT, 3, 3, 0>::get(hit)
-                              : step == 2 ? TqPivot<FMT, W - 1, 2, 0>::get(hit)
-                              : step == 1 ? TqPivot<FMT, W - 1, 1, 0>::get(hit)
-                                          : TqPivot<FMT, W - 1, 0, 0>::get(hit);
-            hit[step] = t > pivot;
-            c |= hit[step] ? (1u << step) : 0u;
+            for (int step = W - 1; step >= 0; step--) {
+                const float pivot = step == 3 ? TqPivot<FMT, 3, 3, 0>::get(hit)
+                                  : step == 2 ? TqPivot<FMT, W - 1, 2, 0>::get(hit)
+                                  : step == 1 ? TqPivot<FMT, W - 1, 1, 0>::get(hit)
+                                              : TqPivot<FMT, W - 1, 0, 0>::get(hit);
+                hit[step] = t > pivot;
+                c |= hit[step] ? (1u << step) : 0u;
+            }
+            bits |= c << (W * i);
         }
-        bits |= c << (W * i);
     }
     return bits;
 }
