@@ -232,6 +232,10 @@ def run(peak_gbs: float, peak_kind: str, only=None, plain=False):
                rows * (NQ + 2 * NKV) * HD * 2 + rows * 2 * NKV * (bpv + 2),
                rows * (2 * NQ + 2 * NKV) * HD * 2 + rows * 2 * NKV * (bpv + 2))
 
+    # the TurboQuant caches' rotation of Q before attention (and of the attention output after it)
+    R.case("kv_rotate Q [14449,28,128]", None, lambda: (rn(rows, NQ, HD),),
+           lambda b, s: _ok(vv.vvb_kv_rotate_dev(b[0], NQ, HD, rows, s)),
+           rows * NQ * HD * 2, rows * NQ * HD * 4)
     # int8 activation quantizers at long-prompt prefill size (14449 rows), with run sums
     def qbufs(K):
         return (torch.empty(rows, K, device=dev, dtype=torch.int8), torch.empty(rows, device=dev, dtype=torch.float32),

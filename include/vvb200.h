@@ -307,6 +307,22 @@ typedef struct vvb_kv_append {
 
 vv_status_t vvb_kv_append_dev(const vvb_kv_append_t* args, void* stream);
 
+/** The other half of a TurboQuant cache: its stored vectors are rotated, so the
+ *  reference rotates Q once before attention and un-rotates the attention
+ *  output after it (src/inference/decoder.c:878-901;
+ *  include/vibevoice/kv_quant.h:89-101 vv_kv_rotate_dev / vv_kv_unrotate_dev,
+ *  kernel src/cuda/kv_quant.cu:173-200). These are those two operations, in
+ *  place on FP16 x [rows, n_heads, head_dim], bit-identical to the reference's
+ *  kernel: per 128-wide head vector a fixed +-1 sign pattern, a 128-point
+ *  Walsh-Hadamard transform and the factor 1 / sqrt(128) (un-rotate: transform
+ *  first, then sign and factor). head_dim must be 128 (VV_ERR_UNSUPPORTED
+ *  otherwise, as the reference); rows == 0 or n_heads == 0 is VV_OK. The names
+ *  carry this library's prefix because the reference defines its own in a file
+ *  this library does not replace (src/cuda/kv_quant.cu holds its attention
+ *  kernels too). */
+vv_status_t vvb_kv_rotate_dev(void* x_fp16, int n_heads, int head_dim, int rows, void* stream);
+vv_status_t vvb_kv_unrotate_dev(void* x_fp16, int n_heads, int head_dim, int rows, void* stream);
+
 /** Final RMSNorm + LM head + greedy argmax in two launches (the reference
  *  issues four: vv_rmsnorm_dev, vv_lm_head_gemv_dev and vv_argmax_dev's two,
  *  src/inference/pipeline.c:1962-1978). x[K] is the last hidden row when

@@ -177,6 +177,15 @@ class _Restated:
             self.lib.orc_tq_rotate128(r.ctypes.data_as(_f32p))
         return out
 
+    def kv_rotate_f16(self, x_f16, inverse=False):
+        """vv_kv_rotate_dev (inverse: vv_kv_unrotate_dev) on FP16 [..., 128]; returns a new array."""
+        self.lib.orc_kv_rotate_f16.argtypes = [_u16p, C.c_size_t, C.c_int]
+        out = np.ascontiguousarray(x_f16, dtype=np.float16).copy()
+        assert out.shape[-1] == 128
+        u = _as_u16(out)
+        assert self.lib.orc_kv_rotate_f16(u.ctypes.data_as(_u16p), out.size // 128, int(bool(inverse))) == 0
+        return out
+
     def kv_store_tq(self, x_f16, ref_f16, fmt, first_row=0, store=None, meta=None):
         """FP16 [n_pos, n_heads, 128] (minus ref [n_heads, 128], in float) -> (codes uint8
         [first_row + n_pos, n_heads * bytes_per_vec], sigma float16 [first_row + n_pos, n_heads]);

@@ -492,6 +492,33 @@ void orc_tq_rotate128(float v[128]) {
     for (int d = 0; d < 128; d++) v[d] *= ORC_WHT_NORM;
 }
 
+/* vv_kv_rotate_dev / vv_kv_unrotate_dev on FP16 head vectors, in place
+ * (src/cuda/kv_quant.cu:173-200): forward = widen, sign flips, transform,
+ * scale, round to FP16; inverse = widen, transform, one multiplication by
+ * (scale * sign), round to FP16. */
+int orc_kv_rotate_f16(uint16_t* x_f16, size_t nvec, int inverse) {
+    if (!x_f16) return ORC_ERR_NULL_PTR;
+    for (size_t n = 0; n < nvec; n++) {
+        uint16_t* p = x_f16 + n * 128;
+        float v[128];
+        for (int d = 0; d < 128; d++) v[d] = orc_half_to_float(p[d]);
+        if (!inverse) {
+            orc_tq_rotate128(v);
+        } else {
+            for (int s = 1; s < 128; s <<= 1)
+                for (int d = 0; d < 128; d++)
+                    if (!(d & s)) {
+                        const float lo = v[d], hi = v[d + s];
+                        v[d] = lo + hi;
+                        v[d + s] = lo - hi;
+                    }
+            for (int d = 0; d < 128; d++) v[d] *= ORC_WHT_NORM * orc_kv_sign(d);
+        }
+        for (int d = 0; d < 128; d++) p[d] = orc_float_to_half_rne(v[d]);
+    }
+    return ORC_OK;
+}
+
 static uint32_t orc_tq_pack4(const float y[4], float inv_sigma, int fmt) {
     uint32_t bits = 0;
     if (fmt == 6) {

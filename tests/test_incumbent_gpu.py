@@ -49,6 +49,8 @@ def libs():
     ref.vv_bias_add_dev.argtypes = [vp, vp, i, i, vp]
     if hasattr(ref, "vv_kv_quant_store_dev"):
         ref.vv_kv_quant_store_dev.argtypes = [vp, vp, vp, vp, vp, vp, vp, C.c_bool, i, i, i, vp, i, i, vp]
+    if hasattr(ref, "vv_kv_rotate_dev"):
+        ref.vv_kv_rotate_dev.argtypes = [vp, i, i, i, vp]
     if hasattr(ref, "vv_kv_store_dev"):
         ref.vv_kv_store_dev.argtypes = [vp, vp, vp, vp, vp, vp, vp, C.c_bool, i, i, i, vp, i, i, vp, vp]
     return vvb200, ref
@@ -247,6 +249,22 @@ def test_tq4_kv_append_vs_incumbent(libs):
                                    NKV, HD, 0, None, rows, fmt, None, s) == 0
     theirs = time_graph(ref_seq, n)
     record(f"bias + rope + 4-bit TurboQuant kv store [{rows},28+4+4,128]", ours, theirs)
+
+
+def test_kv_rotate_vs_incumbent(libs):
+    """The Hadamard rotation of Q for attention over a TurboQuant cache, [14449, 28, 128] in place."""
+    vv, ref = libs
+    if not hasattr(ref, "vv_kv_rotate_dev"):
+        pytest.skip("the reference's kv_quant.cu is not in the compiled library")
+    rows = 14449
+    n = nsets(rows * NQ * HD * 2)
+    qs = [rn(rows, NQ, HD) for _ in range(n)]
+    ours = time_graph(lambda k, s: vv.vvb_kv_rotate_dev(qs[k], NQ, HD, rows, s), n)
+
+    def ref_fn(k, s):
+        assert ref.vv_kv_rotate_dev(p(qs[k]), NQ, HD, rows, s) == 0
+    theirs = time_graph(ref_fn, n)
+    record(f"kv_rotate Q [{rows},28,128]", ours, theirs)
 
 
 def test_lm_head_vs_incumbent(libs):

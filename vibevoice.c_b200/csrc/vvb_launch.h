@@ -50,6 +50,10 @@ int vvbk_rope_append(void* q, void* k, const void* v,
                      const float* inv_freq, int keep_k, int kv_format, const void* k_ref,
                      const int* page_table, void* k_meta, void* v_meta, void* stream);
 
+/* The TurboQuant caches' rotation of Q / un-rotation of the attention output
+ * (csrc/kv_rotate.cu): nvec head vectors of 128 halves, in place. */
+int vvbk_kv_rotate(void* x, size_t nvec, int inverse, void* stream);
+
 /* SwiGLU (csrc/swiglu.cu). Flat: gate/up/out of n elements. Fused: rows of
  * [gate | up] with 2*inter halves per row. */
 int vvbk_swiglu(const void* gate, const void* up, void* out, size_t n, void* stream);

@@ -63,6 +63,24 @@ vv_status_t vvb_rope_qk_dev(void* q, void* k, int rows, int n_q_heads, int n_kv_
                                position_offset, d_position, inv_freq, stream));
 }
 
+static vv_status_t kv_rotate_common(void* x, int n_heads, int head_dim, int rows, int inverse, void* stream) {
+    if (!x) return VV_ERR_NULL_PTR;
+    if (n_heads < 0 || rows < 0 || head_dim <= 0) return VV_ERR_INVALID_ARG;
+    if (head_dim != 128) return VV_ERR_UNSUPPORTED;       /* as the reference (src/cuda/kv_quant.cu:477) */
+    if (((uintptr_t)x & 1u) != 0) return VV_ERR_INVALID_ARG;
+    const size_t nvec = (size_t)rows * (size_t)n_heads;
+    if (nvec == 0) return VV_OK;
+    return from_cuda(vvbk_kv_rotate(x, nvec, inverse, stream));
+}
+
+vv_status_t vvb_kv_rotate_dev(void* x, int n_heads, int head_dim, int rows, void* stream) {
+    return kv_rotate_common(x, n_heads, head_dim, rows, 0, stream);
+}
+
+vv_status_t vvb_kv_unrotate_dev(void* x, int n_heads, int head_dim, int rows, void* stream) {
+    return kv_rotate_common(x, n_heads, head_dim, rows, 1, stream);
+}
+
 vv_status_t vvb_kv_append_dev(const vvb_kv_append_t* a, void* stream) {
     if (!a) return VV_ERR_NULL_PTR;
     if (!a->q || !a->k || !a->v || !a->k_store || !a->v_store) return VV_ERR_NULL_PTR;

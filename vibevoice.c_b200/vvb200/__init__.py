@@ -73,6 +73,8 @@ class KvAppend(C.Structure):
 # name -> (restype, argtypes): every symbol include/vvb200.h declares
 SIGNATURES = {
     "vvb_kv_append_dev": (_i, [C.POINTER(KvAppend), _vp]),
+    "vvb_kv_rotate_dev": (_i, [_vp, _i, _i, _i, _vp]),
+    "vvb_kv_unrotate_dev": (_i, [_vp, _i, _i, _i, _vp]),
     "vv_embedding_dev": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "vv_rmsnorm_dev": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp]),
     "vv_rope_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _f, _vp]),
@@ -287,6 +289,16 @@ def vvb_kv_append_dev(q, k, v, k_store, v_store, rows, n_q_heads, n_kv_heads, he
                  _ptr(k_ref), _ptr(page_table), _ptr(d_position), rows, n_q_heads, n_kv_heads, head_dim,
                  position_offset, cache_offset, theta, kv_format, keep_k, _ptr(k_meta), _ptr(v_meta))
     return _lib.vvb_kv_append_dev(C.byref(a), _stream(stream))
+
+
+def vvb_kv_rotate_dev(x, n_heads, head_dim, rows, stream=None) -> int:
+    """Q before attention over a TurboQuant cache: sign pattern, 128-point Hadamard transform, 1/sqrt(128); in place."""
+    return _lib.vvb_kv_rotate_dev(_ptr(x), n_heads, head_dim, rows, _stream(stream))
+
+
+def vvb_kv_unrotate_dev(x, n_heads, head_dim, rows, stream=None) -> int:
+    """The attention output after it: the inverse of vvb_kv_rotate_dev; in place."""
+    return _lib.vvb_kv_unrotate_dev(_ptr(x), n_heads, head_dim, rows, _stream(stream))
 
 
 def vvb_rope_qk_append_fp8_dev(q, k, v, q_bias, k_bias, v_bias, k_store, v_store, k_ref, rows, n_q_heads,
