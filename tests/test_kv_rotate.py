@@ -120,7 +120,7 @@ def same_bits(a, b):
 
 
 @gpu
-@pytest.mark.parametrize("rows,heads", [(1, 28), (300, 28), (2048, 4), (7, 3), (33, 1), (4099, 28)])
+@pytest.mark.parametrize("rows,heads", [(1, 28), (300, 28), (2048, 4), (7, 3), (33, 1), (611, 1), (171, 3), (4099, 28)])
 @pytest.mark.parametrize("inverse", [False, True])
 def test_rotate_equals_oracle_and_the_live_reference_kernel(vv, refk, orc, rows, heads, inverse):
     x = stress_input(rows, heads, rows * 3 + heads)

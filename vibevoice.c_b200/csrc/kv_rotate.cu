@@ -6,14 +6,19 @@
  * per key (src/inference/decoder.c:878-901, include/vibevoice/kv_quant.h:89-101;
  * kernel src/cuda/kv_quant.cu:173-200, entry points :473-494).
  *
- * One 128-wide head vector per warp, lane L holding values 4L .. 4L+3 (one
- * 8-byte load), in place:
+ * Per 128-wide head vector, in place:
  *   forward   v = half -> float; v *= sign(d); WHT128; v *= 1/sqrt(128); -> half
  *   inverse   WHT128; v *= (1/sqrt(128)) * sign(d); -> half
- * in the reference kernel's order of operations, so the bytes are its bytes
- * (the sign factor is +-1: both multiplications round once, whichever way the
- * compiler associates them). HBM-bound: 512 bytes per head vector; a warp keeps
- * kVecs vectors' loads in flight.
+ * A butterfly stage computes (lo + hi, lo - hi) for the pairs (d, d + stride) whatever
+ * thread holds them, so the results are the reference kernel's bits for any
+ * distribution of the vector over lanes. Here EIGHT lanes share a vector, 16
+ * consecutive values each (two 16-byte loads): four stages run inside the lane and
+ * three by shuffle, against two and five with four values per lane -- the kernel is
+ * bound by instruction issue, and the shuffle stages cost twice the in-lane ones. The
+ * sign pattern is applied to the FP16 bits (a sign flip commutes with every rounding):
+ * one XOR per pair of values, on the input going forward, on the output coming back.
+ * A warp takes four consecutive vectors (1 KB) per step and has two steps' loads in
+ * flight. HBM traffic: 512 bytes per head vector.
  */
 #include "tq_kv.cuh"
 #include "vvb_launch.h"
@@ -24,59 +29,125 @@ namespace vvb {
 
 constexpr int kRotThreads = 256;
 constexpr int kRotWarps = kRotThreads / 32;
-constexpr int kRotVecs = 4;            /* head vectors a warp has in flight */
+constexpr int kRotSteps = 2;           /* groups of four vectors a warp has in flight */
 
-template <bool INVERSE, bool ALIGNED>
+/* 16 values of one vector in a lane: stages of stride 1..8 in the lane, 16..64 against
+ * lanes ^1, ^2, ^4 of the eight that share the vector. */
+__device__ __forceinline__ void wht128_16(float (&v)[16], int lane) {
+#pragma unroll
+    for (int s = 1; s < 16; s <<= 1)
+#pragma unroll
+        for (int d = 0; d < 16; d++)
+            if (!(d & s)) {
+                const float lo = v[d], hi = v[d + s];
+                v[d] = __fadd_rn(lo, hi);
+                v[d + s] = __fsub_rn(lo, hi);
+            }
+#pragma unroll
+    for (int m = 1; m < 8; m <<= 1) {
+        const float own = (lane & m) ? -1.0f : 1.0f;
+        float o[16];
+#pragma unroll
+        for (int d = 0; d < 16; d++) o[d] = __shfl_xor_sync(0xffffffffu, v[d], m);
+#pragma unroll
+        for (int d = 0; d < 16; d++) v[d] = __fmaf_rn(v[d], own, o[d]);     /* other -+ own, one rounding */
+    }
+}
+
+template <bool INVERSE>
 __global__ void __launch_bounds__(kRotThreads)
-kv_rotate_kernel(__half* x, size_t nvec) {
+kv_rotate_kernel(vec16* x, size_t nvec) {
     pdl_wait();
     pdl_trigger();
     const int lane = threadIdx.x & 31;
-    const size_t first = ((size_t)blockIdx.x * kRotWarps + (threadIdx.x >> 5)) * kRotVecs;
-    float sgn[4];
+    const int sub = lane & 7;                                   /* which 16 values of the vector */
+    /* sign bits of values 16 sub .. 16 sub + 15 as FP16 sign masks, two values per word */
+    uint32_t flip[8];
 #pragma unroll
-    for (int i = 0; i < 4; i++) sgn[i] = tq_sign(4 * lane + i);
-
-    float v[kRotVecs][4];
-    bool live[kRotVecs];
+    for (int w = 0; w < 8; w++) {
+        const uint32_t lo = tq_sign(16 * sub + 2 * w) < 0.0f ? 0x8000u : 0u;
+        const uint32_t hi = tq_sign(16 * sub + 2 * w + 1) < 0.0f ? 0x80000000u : 0u;
+        flip[w] = lo | hi;
+    }
+    /* vector index of this lane in step n: warps take consecutive groups of 4 vectors */
+    const size_t first = ((size_t)blockIdx.x * kRotWarps + (threadIdx.x >> 5)) * (4 * kRotSteps) + (lane >> 3);
+    vec16 raw[kRotSteps][2];
+    bool live[kRotSteps];
 #pragma unroll
-    for (int n = 0; n < kRotVecs; n++) {
-        live[n] = first + n < nvec;                       /* warp-uniform */
-        __half* p = x + (first + n) * 128 + 4 * lane;
+    for (int n = 0; n < kRotSteps; n++) {
+        const size_t vec = first + 4 * n;
+        live[n] = vec < nvec;
         if (live[n]) {
-            if (ALIGNED) {
-                const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(p));
-                const float2 a = unpack2(raw.x), b = unpack2(raw.y);
-                v[n][0] = a.x; v[n][1] = a.y; v[n][2] = b.x; v[n][3] = b.y;
-            } else {
+            const vec16* p = x + vec * 16 + 2 * sub;            /* a vector is 16 x 16 bytes */
+            raw[n][0] = ld_stream(p);
+            raw[n][1] = ld_stream(p + 1);
+        } else {
+            raw[n][0] = raw[n][1] = make_uint4(0, 0, 0, 0);
+        }
+    }
 #pragma unroll
-                for (int i = 0; i < 4; i++) v[n][i] = __half2float(p[i]);
-            }
+    for (int n = 0; n < kRotSteps; n++) {
+        /* a whole warp runs the shuffles; lanes whose vector lies beyond the end carry zeros */
+        uint32_t* w = reinterpret_cast<uint32_t*>(&raw[n][0]);
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float2 f = unpack2(INVERSE ? w[i] : (w[i] ^ flip[i]));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+        wht128_16(v, lane);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t packed = pack2(__fmul_rn(v[2 * i], kTqWhtNorm), __fmul_rn(v[2 * i + 1], kTqWhtNorm));
+            w[i] = INVERSE ? (packed ^ flip[i]) : packed;
+        }
+        if (live[n]) {
+            vec16* p = x + (first + 4 * n) * 16 + 2 * sub;
+            st_stream(p, raw[n][0]);
+            st_stream(p + 1, raw[n][1]);
+        }
+    }
+}
+
+/* The plain statement, a vector per warp, lane L holding values 4L .. 4L+3: for pointers
+ * that are not 16-byte aligned (ALIGNED8 false: half by half) and for a handful of vectors
+ * (a decode step's 28 heads), where the sign masks of the form above cost more than they
+ * save. */
+template <bool INVERSE, bool ALIGNED8>
+__global__ void __launch_bounds__(kRotThreads)
+kv_rotate_small_kernel(__half* x, size_t nvec) {
+    pdl_wait();
+    pdl_trigger();
+    const int lane = threadIdx.x & 31;
+    const size_t vec = (size_t)blockIdx.x * kRotWarps + (threadIdx.x >> 5);
+    const bool live = vec < nvec;                               /* warp-uniform */
+    __half* p = x + (live ? vec : 0) * 128 + 4 * lane;
+    float v[1][4] = {{0.0f, 0.0f, 0.0f, 0.0f}};
+    if (live) {
+        if (ALIGNED8) {
+            const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(p));
+            const float2 a = unpack2(raw.x), b = unpack2(raw.y);
+            v[0][0] = a.x; v[0][1] = a.y; v[0][2] = b.x; v[0][3] = b.y;
         } else {
 #pragma unroll
-            for (int i = 0; i < 4; i++) v[n][i] = 0.0f;
+            for (int i = 0; i < 4; i++) v[0][i] = __half2float(p[i]);
         }
     }
     if (!INVERSE) {
 #pragma unroll
-        for (int n = 0; n < kRotVecs; n++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) v[n][i] = __fmul_rn(v[n][i], sgn[i]);
+        for (int i = 0; i < 4; i++) v[0][i] = __fmul_rn(v[0][i], tq_sign(4 * lane + i));
     }
-    tq_wht128<kRotVecs>(v, lane);                          /* every lane of the warp takes part */
+    tq_wht128<1>(v, lane);
+    if (!live) return;
 #pragma unroll
-    for (int n = 0; n < kRotVecs; n++) {
+    for (int i = 0; i < 4; i++)
+        v[0][i] = __fmul_rn(v[0][i], INVERSE ? __fmul_rn(kTqWhtNorm, tq_sign(4 * lane + i)) : kTqWhtNorm);
+    if (ALIGNED8) {
+        __stcs(reinterpret_cast<uint2*>(p), make_uint2(pack2(v[0][0], v[0][1]), pack2(v[0][2], v[0][3])));
+    } else {
 #pragma unroll
-        for (int i = 0; i < 4; i++)
-            v[n][i] = __fmul_rn(v[n][i], INVERSE ? __fmul_rn(kTqWhtNorm, sgn[i]) : kTqWhtNorm);
-        if (!live[n]) continue;
-        __half* p = x + (first + n) * 128 + 4 * lane;
-        if (ALIGNED) {
-            __stcs(reinterpret_cast<uint2*>(p), make_uint2(pack2(v[n][0], v[n][1]), pack2(v[n][2], v[n][3])));
-        } else {
-#pragma unroll
-            for (int i = 0; i < 4; i++) p[i] = __float2half_rn(v[n][i]);
-        }
+        for (int i = 0; i < 4; i++) p[i] = __float2half_rn(v[0][i]);
     }
 }
 
@@ -89,17 +160,23 @@ using namespace vvb;
 extern "C" int vvbk_kv_rotate(void* x, size_t nvec, int inverse, void* stream) {
     if (nvec == 0) return (int)cudaSuccess;
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t per_cta = (size_t)kRotWarps * kRotVecs;
+    constexpr size_t kSmall = 512;                       /* vectors: below this the plain form is faster */
+    const bool aligned16 = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    const bool aligned8 = (reinterpret_cast<uintptr_t>(x) & 7u) == 0;
+    const bool fast = aligned16 && nvec >= kSmall;
+    const size_t per_cta = fast ? (size_t)kRotWarps * 4 * kRotSteps : (size_t)kRotWarps;
     const size_t ctas = (nvec + per_cta - 1) / per_cta;
     if (ctas > 0x7fffffffull) return (int)cudaErrorInvalidValue;
-    const bool aligned = (reinterpret_cast<uintptr_t>(x) & 7u) == 0;
     const dim3 grid((unsigned)ctas), block(kRotThreads);
-    if (inverse) {
-        if (aligned) launch_pdl(kv_rotate_kernel<true, true>, grid, block, 0, s, (__half*)x, nvec);
-        else launch_pdl(kv_rotate_kernel<true, false>, grid, block, 0, s, (__half*)x, nvec);
+    if (fast) {
+        if (inverse) launch_pdl(kv_rotate_kernel<true>, grid, block, 0, s, (vec16*)x, nvec);
+        else launch_pdl(kv_rotate_kernel<false>, grid, block, 0, s, (vec16*)x, nvec);
+    } else if (aligned8) {
+        if (inverse) launch_pdl(kv_rotate_small_kernel<true, true>, grid, block, 0, s, (__half*)x, nvec);
+        else launch_pdl(kv_rotate_small_kernel<false, true>, grid, block, 0, s, (__half*)x, nvec);
     } else {
-        if (aligned) launch_pdl(kv_rotate_kernel<false, true>, grid, block, 0, s, (__half*)x, nvec);
-        else launch_pdl(kv_rotate_kernel<false, false>, grid, block, 0, s, (__half*)x, nvec);
+        if (inverse) launch_pdl(kv_rotate_small_kernel<true, false>, grid, block, 0, s, (__half*)x, nvec);
+        else launch_pdl(kv_rotate_small_kernel<false, false>, grid, block, 0, s, (__half*)x, nvec);
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
