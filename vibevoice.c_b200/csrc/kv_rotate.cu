@@ -62,13 +62,13 @@ kv_rotate_kernel(vec16* x, size_t nvec) {
     const int lane = threadIdx.x & 31;
     const int sub = lane & 7;                                   /* which 16 values of the vector */
     /* sign bits of values 16 sub .. 16 sub + 15 as FP16 sign masks, two values per word */
+    constexpr uint32_t s0 = tq_sign_word(0), s1 = tq_sign_word(1), s2 = tq_sign_word(2), s3 = tq_sign_word(3);
+    const uint32_t word = (sub & 4) ? ((sub & 2) ? s3 : s2) : ((sub & 2) ? s1 : s0);
+    const uint32_t mine = (sub & 1) ? (word >> 16) : word;      /* low 16 bits: this lane's values */
     uint32_t flip[8];
 #pragma unroll
-    for (int w = 0; w < 8; w++) {
-        const uint32_t lo = tq_sign(16 * sub + 2 * w) < 0.0f ? 0x8000u : 0u;
-        const uint32_t hi = tq_sign(16 * sub + 2 * w + 1) < 0.0f ? 0x80000000u : 0u;
-        flip[w] = lo | hi;
-    }
+    for (int w = 0; w < 8; w++)
+        flip[w] = ((mine << (15 - 2 * w)) & 0x8000u) | ((mine << (30 - 2 * w)) & 0x80000000u);
     /* vector index of this lane in step n: warps take consecutive groups of 4 vectors */
     const size_t first = ((size_t)blockIdx.x * kRotWarps + (threadIdx.x >> 5)) * (4 * kRotSteps) + (lane >> 3);
     vec16 raw[kRotSteps][2];

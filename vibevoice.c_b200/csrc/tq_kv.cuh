@@ -54,6 +54,20 @@ __device__ __forceinline__ float tq_sign(int d) {
     return (h & 1u) ? -1.0f : 1.0f;
 }
 
+/* The same pattern as bits, worked out by the compiler: bit (d & 31) of word d >> 5 is set
+ * where the sign is negative. */
+__host__ __device__ constexpr uint32_t tq_sign_word(int w) {
+    uint32_t bits = 0;
+    for (int b = 0; b < 32; b++) {
+        uint32_t h = (uint32_t)(32 * w + b) * 2654435761u + 0x9E3779B9u;
+        h ^= h >> 15;
+        h *= 0x85EBCA6Bu;
+        h ^= h >> 13;
+        bits |= (h & 1u) << b;
+    }
+    return bits;
+}
+
 /* The levels (src/cuda/kv_codec.cuh:46-62). Scalar formats compare against the
  * decision thresholds 0.5f * (level[j] + level[j + 1]), which the reference forms
  * in float at run time; as compile-time constants they are the same floats (one
@@ -259,10 +273,13 @@ __device__ __forceinline__ void tq_store_vecs(float (&v)[NV][4], int lane, uint8
                                               __half* const (&meta)[NV], const bool (&live)[NV],
                                               const TqCells* cells) {
     constexpr int NB = TqBits<FMT>::N;
-    const int d0 = lane * 4;
+    /* the signs of values 4 lane .. 4 lane + 3 out of the compile-time bit pattern */
+    constexpr uint32_t s0 = tq_sign_word(0), s1 = tq_sign_word(1), s2 = tq_sign_word(2), s3 = tq_sign_word(3);
+    const uint32_t word = (lane & 16) ? ((lane & 8) ? s3 : s2) : ((lane & 8) ? s1 : s0);
+    const uint32_t mine = word >> (4 * (lane & 7));
     float sgn[4];
 #pragma unroll
-    for (int i = 0; i < 4; i++) sgn[i] = tq_sign(d0 + i);
+    for (int i = 0; i < 4; i++) sgn[i] = ((mine >> i) & 1u) ? -1.0f : 1.0f;
 #pragma unroll
     for (int n = 0; n < NV; n++)
 #pragma unroll
