@@ -303,6 +303,55 @@ def test_extreme_and_nonfinite_vectors_match_the_reference_kernel(vv, refk, fmt,
 
 
 @gpu
+def test_fuzz_tq_append_against_the_reference_kernel(vv, refk):
+    """Random head counts (K columns that straddle the kernel's column chunks, KV head counts that do
+    not divide its warp count), row counts, formats, paged or not, with and without biases and
+    reference key: the fused launch's codes and sigmas against the reference's store kernel fed the
+    FP16 K this library leaves in place (keep_k) and the biased V."""
+    rng = np.random.default_rng(2024)
+    bpv_of = {3: 64, 4: 48, 5: 32, 6: 24}
+    for case in range(24):
+        nq, nkv = int(rng.integers(1, 41)), int(rng.integers(1, 9))
+        rows = int(rng.choice([1, 2, 5, 64, 65, 200]))
+        fmt = int(rng.integers(3, 7))
+        bpv = bpv_of[fmt]
+        paged = bool(rng.integers(2))
+        first = int(rng.choice([0, 3, 64, 100]))
+        pos0 = int(rng.choice([0, 7, 5000]))
+        f16 = lambda *s, sc=1.0: (rng.standard_normal(s) * sc).astype(np.float16)
+        q, k, v = f16(rows, nq, HD), f16(rows, nkv, HD, sc=1.5), f16(rows, nkv, HD, sc=0.4)
+        qb = f16(nq * HD, sc=0.3) if rng.integers(2) else None
+        kb = f16(nkv * HD, sc=0.3) if rng.integers(2) else None
+        vb = f16(nkv * HD, sc=0.3) if rng.integers(2) else None
+        kref = f16(nkv, HD, sc=0.5) if rng.integers(2) else None
+        n_pages = (first + rows + 63) // 64
+        pool = n_pages + 3
+        table = dev(rng.permutation(pool)[:n_pages].astype(np.int32)) if paged else None
+        cache_rows = pool * 64 if paged else first + rows + 2
+        fill = lambda w, dt=torch.uint8: torch.full((cache_rows, w), 0xA5 if dt == torch.uint8 else 7.0, dtype=dt, device="cuda")
+        opt = lambda a: dev(a) if a is not None else None
+        dq, dk, dv = dev(q), dev(k), dev(v)
+        ks, vs, km, vm = fill(nkv * bpv), fill(nkv * bpv), fill(nkv, torch.float16), fill(nkv, torch.float16)
+        tag = (case, nq, nkv, rows, fmt, paged, first)
+        st = vv.vvb_kv_append_dev(dq, dk, dv, ks, vs, rows, nq, nkv, HD, q_bias=opt(qb), k_bias=opt(kb), v_bias=opt(vb),
+                                  k_ref=opt(kref), page_table=table, position_offset=pos0, cache_offset=first,
+                                  kv_format=fmt, keep_k=1, k_meta=km, v_meta=vm)
+        assert st == 0, tag + (st,)
+        v16 = dev(v)
+        if vb is not None:
+            assert vv.vv_bias_add_dev(v16, dev(vb), rows, nkv * HD) == 0
+        rks, rvs, rkm, rvm = fill(nkv * bpv), fill(nkv * bpv), fill(nkv, torch.float16), fill(nkv, torch.float16)
+        st = refk.vv_kv_store_dev(p(dk), p(v16), p(rks), p(rvs), p(rkm), p(rvm), p(opt(kref)), False, nkv, HD, first,
+                                  None, rows, fmt, p(table), None)
+        assert st == 0, tag
+        torch.cuda.synchronize()
+        for got, want, what in ((ks, rks, "K codes"), (vs, rvs, "V codes"),
+                                (km.view(torch.int16), rkm.view(torch.int16), "K sigma"),
+                                (vm.view(torch.int16), rvm.view(torch.int16), "V sigma")):
+            assert torch.equal(got, want), tag + (what,)
+
+
+@gpu
 def test_tq_argument_checks(vv):
     x = torch.zeros(4, 4, 128, dtype=torch.float16, device="cuda")
     q = torch.zeros(4, 28, 128, dtype=torch.float16, device="cuda")
