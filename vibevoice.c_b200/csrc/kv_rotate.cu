@@ -31,29 +31,6 @@ constexpr int kRotThreads = 256;
 constexpr int kRotWarps = kRotThreads / 32;
 constexpr int kRotSteps = 2;           /* groups of four vectors a warp has in flight */
 
-/* 16 values of one vector in a lane: stages of stride 1..8 in the lane, 16..64 against
- * lanes ^1, ^2, ^4 of the eight that share the vector. */
-__device__ __forceinline__ void wht128_16(float (&v)[16], int lane) {
-#pragma unroll
-    for (int s = 1; s < 16; s <<= 1)
-#pragma unroll
-        for (int d = 0; d < 16; d++)
-            if (!(d & s)) {
-                const float lo = v[d], hi = v[d + s];
-                v[d] = __fadd_rn(lo, hi);
-                v[d + s] = __fsub_rn(lo, hi);
-            }
-#pragma unroll
-    for (int m = 1; m < 8; m <<= 1) {
-        const float own = (lane & m) ? -1.0f : 1.0f;
-        float o[16];
-#pragma unroll
-        for (int d = 0; d < 16; d++) o[d] = __shfl_xor_sync(0xffffffffu, v[d], m);
-#pragma unroll
-        for (int d = 0; d < 16; d++) v[d] = __fmaf_rn(v[d], own, o[d]);     /* other -+ own, one rounding */
-    }
-}
-
 template <bool INVERSE>
 __global__ void __launch_bounds__(kRotThreads)
 kv_rotate_kernel(vec16* x, size_t nvec) {
@@ -61,14 +38,8 @@ kv_rotate_kernel(vec16* x, size_t nvec) {
     pdl_trigger();
     const int lane = threadIdx.x & 31;
     const int sub = lane & 7;                                   /* which 16 values of the vector */
-    /* sign bits of values 16 sub .. 16 sub + 15 as FP16 sign masks, two values per word */
-    constexpr uint32_t s0 = tq_sign_word(0), s1 = tq_sign_word(1), s2 = tq_sign_word(2), s3 = tq_sign_word(3);
-    const uint32_t word = (sub & 4) ? ((sub & 2) ? s3 : s2) : ((sub & 2) ? s1 : s0);
-    const uint32_t mine = (sub & 1) ? (word >> 16) : word;      /* low 16 bits: this lane's values */
-    uint32_t flip[8];
-#pragma unroll
-    for (int w = 0; w < 8; w++)
-        flip[w] = ((mine << (15 - 2 * w)) & 0x8000u) | ((mine << (30 - 2 * w)) & 0x80000000u);
+    uint32_t flip[8];                                           /* FP16 sign masks of this lane's 16 values */
+    tq_flips16(sub, flip);
     /* vector index of this lane in step n: warps take consecutive groups of 4 vectors */
     const size_t first = ((size_t)blockIdx.x * kRotWarps + (threadIdx.x >> 5)) * (4 * kRotSteps) + (lane >> 3);
     vec16 raw[kRotSteps][2];
@@ -96,7 +67,7 @@ kv_rotate_kernel(vec16* x, size_t nvec) {
             v[2 * i] = f.x;
             v[2 * i + 1] = f.y;
         }
-        wht128_16(v, lane);
+        tq_wht128_16(v, lane);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             const uint32_t packed = pack2(__fmul_rn(v[2 * i], kTqWhtNorm), __fmul_rn(v[2 * i + 1], kTqWhtNorm));

@@ -56,7 +56,6 @@ namespace vvb {
 extern std::atomic<uint64_t> g_launches;
 
 constexpr int kVRowsPerCta = 32;
-constexpr int kTqPair = 2;           /* TurboQuant: head vectors a warp works on side by side */
 
 /* CTAs per SM the FP16 variant is compiled for (the FP8 variants take 3: at 4
  * they spill and run 61.7 instead of 48.0 us; the FP16 variant measures 43.8 us
@@ -122,51 +121,55 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
         const int items = min(kVRowsPerCta, a.rows - row0v) * cols_v;
         const int cache_first_v = (a.d_position != nullptr) ? *a.d_position : A.cache_offset;
         if constexpr (kv_is_tq(FMT)) {
-            /* a head vector (128 values) per warp: lane L takes values 4L .. 4L+3 */
+            /* eight lanes to a head vector (tq_store16): a warp takes four consecutive vectors a
+             * step, each lane two 16-byte pieces of its vector, and has two steps' loads in flight */
             constexpr int BPV = tq_bytes_per_vec(FMT);
-            constexpr int kU = 4;
-            const int warp = t >> 5, lane = t & 31;
+            constexpr int kU = 2;
+            constexpr int kWarps = kRopeThreads / 32;
+            const int warp = t >> 5, lane = t & 31, sub = lane & 7;
             const int nvecs = min(kVRowsPerCta, a.rows - row0v) * a.n_kv;
             if constexpr (TqUsesCells<FMT>::value) __syncthreads();       /* the cell table */
-            const uint2* vsrc = reinterpret_cast<const uint2*>(A.v) + (size_t)row0v * a.n_kv * 32;
-            /* (row, head) of vector idx = warp + 8 * n, kept by stepping instead of dividing */
-            constexpr int kWarps = kRopeThreads / 32;
-            const int step_r = kWarps / a.n_kv, step_h = kWarps - step_r * a.n_kv;
-            int rl = warp / a.n_kv, h = warp - rl * a.n_kv;
-            for (int base = warp; base < nvecs; base += kWarps * kU) {
-                uint2 x[kU];
+            uint32_t flip[8];
+            tq_flips16(sub, flip);
+            const vec16* vsrc = A.v + (size_t)row0v * a.n_kv * 16;       /* a vector is 16 pieces */
+            /* (row, head) of this lane's vector idx = 4 warp + (lane >> 3) + 32 n, by stepping */
+            const int step_r = (4 * kWarps) / a.n_kv, step_h = 4 * kWarps - step_r * a.n_kv;
+            const int idx0 = 4 * warp + (lane >> 3);
+            int rl = idx0 / a.n_kv, h = idx0 - rl * a.n_kv;
+            for (int base = 4 * warp; base < nvecs; base += 4 * kWarps * kU) {      /* warp-uniform */
+                vec16 x[kU][2];
 #pragma unroll
                 for (int j = 0; j < kU; j++) {
-                    const int idx = base + j * kWarps;
-                    if (idx < nvecs) x[j] = __ldcs(vsrc + (size_t)idx * 32 + lane);
+                    const int idx = base + j * 4 * kWarps + (lane >> 3);
+                    if (idx < nvecs) {
+                        x[j][0] = ld_stream(vsrc + (size_t)idx * 16 + 2 * sub);
+                        x[j][1] = ld_stream(vsrc + (size_t)idx * 16 + 2 * sub + 1);
+                    } else {
+                        x[j][0] = x[j][1] = make_uint4(0, 0, 0, 0);
+                    }
                 }
 #pragma unroll
-                for (int j0 = 0; j0 < kU; j0 += kTqPair) {
-                    float v4[kTqPair][4];
-                    uint8_t* dstp[kTqPair];
-                    __half* metap[kTqPair];
-                    bool livep[kTqPair];
-#pragma unroll
-                    for (int n = 0; n < kTqPair; n++) {
-                        const int idx = base + (j0 + n) * kWarps;
-                        livep[n] = idx < nvecs;               /* warp-uniform */
-                        uint2 xv = livep[n] ? x[j0 + n] : make_uint2(0u, 0u);
-                        if (A.v_bias && livep[n]) {
-                            const uint2 b = __ldg(reinterpret_cast<const uint2*>(A.v_bias) + h * 32 + lane);
-                            xv.x = hadd2_bits(xv.x, b.x);
-                            xv.y = hadd2_bits(xv.y, b.y);
-                        }
-                        const float2 f0 = unpack2(xv.x), f1 = unpack2(xv.y);
-                        v4[n][0] = f0.x; v4[n][1] = f0.y; v4[n][2] = f1.x; v4[n][3] = f1.y;
-                        const size_t at = livep[n]
-                            ? cache_row(PAGED ? A.page_table : nullptr, cache_first_v + row0v + rl) * a.n_kv + h : 0;
-                        dstp[n] = reinterpret_cast<uint8_t*>(A.v_cache) + at * BPV;
-                        metap[n] = A.v_meta + at;
-                        h += step_h;
-                        rl += step_r;
-                        if (h >= a.n_kv) { h -= a.n_kv; rl++; }
+                for (int j = 0; j < kU; j++) {
+                    if (base + j * 4 * kWarps >= nvecs) break;                    /* warp-uniform */
+                    const int idx = base + j * 4 * kWarps + (lane >> 3);
+                    const bool live = idx < nvecs;
+                    if (A.v_bias && live) {
+                        x[j][0] = add_bias_vec(x[j][0], __ldg(A.v_bias + h * 16 + 2 * sub));
+                        x[j][1] = add_bias_vec(x[j][1], __ldg(A.v_bias + h * 16 + 2 * sub + 1));
                     }
-                    if (livep[0]) tq_store_vecs<FMT, kTqPair>(v4, lane, dstp, metap, livep, tq_cells);
+                    const uint32_t* w = reinterpret_cast<const uint32_t*>(&x[j][0]);
+                    float v16[16];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const float2 f = unpack2(w[i] ^ flip[i]);
+                        v16[2 * i] = f.x;
+                        v16[2 * i + 1] = f.y;
+                    }
+                    const size_t at = live ? cache_row(PAGED ? A.page_table : nullptr, cache_first_v + row0v + rl) * a.n_kv + h : 0;
+                    tq_store16<FMT>(v16, lane, reinterpret_cast<uint8_t*>(A.v_cache) + at * BPV, A.v_meta + at, live, tq_cells);
+                    h += step_h;
+                    rl += step_r;
+                    if (h >= a.n_kv) { h -= a.n_kv; rl++; }
                 }
             }
             return;
@@ -349,38 +352,48 @@ rope_append_kernel(const __grid_constant__ RopeAppendArgs A) {
             const int warp = t >> 5, lane = t & 31;
             const int heads = kcols / a.hvn;                       /* K heads of this column chunk */
             const int head0 = first_k_col / a.hvn - a.n_q;         /* first of them, as a KV head index */
-            /* lane L's values 4L .. 4L+3: half (d >= 64), vector inside the half, first or second 8 bytes of it */
-            const int half_sel = lane >> 4, vsel = (lane & 15) >> 1, part = lane & 1;
+            /* eight lanes to a head vector (tq_store16), four vectors per warp and step: this lane's
+             * values 16 sub .. 16 sub + 15 are two 16-byte pieces of the low (sub < 4) or high half */
+            const int sub = lane & 7, half_sel = sub >> 2, vsel = 2 * (sub & 3);
             constexpr int kWarps = kRopeThreads / 32;
-            const int step_r = kWarps / heads, step_h = kWarps - step_r * heads;
-            int rl = warp / heads, hk = warp - rl * heads;
-            for (int idx = warp; idx < nrows * heads; idx += kWarps * kTqPair) {
-                float v4[kTqPair][4];
-                uint8_t* dstp[kTqPair];
-                __half* metap[kTqPair];
-                bool livep[kTqPair];
+            uint32_t flip[8];
+            tq_flips16(sub, flip);
+            const int total = nrows * heads;
+            const int step_r = (4 * kWarps) / heads, step_h = 4 * kWarps - step_r * heads;
+            const int idx0 = 4 * warp + (lane >> 3);
+            int rl = idx0 / heads, hk = idx0 - rl * heads;
+            for (int base = 4 * warp; base < total; base += 4 * kWarps) {          /* warp-uniform */
+                const bool live = base + (lane >> 3) < total;
+                const int rs = live ? rl : 0, hs = live ? hk : 0;
+                const vec16* src16 = &k_stage[(rs * 2 + half_sel) * kcols + hs * a.hvn + vsel];
+                const vec16 x0 = src16[0], x1 = src16[1];
+                const int h = head0 + hs;
+                const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&x0);
+                const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&x1);
+                float v16[16];
 #pragma unroll
-                for (int n = 0; n < kTqPair; n++) {
-                    livep[n] = idx + n * kWarps < nrows * heads;      /* warp-uniform */
-                    const int rs = livep[n] ? rl : 0, hs = livep[n] ? hk : 0;
-                    const uint2 raw = reinterpret_cast<const uint2*>(&k_stage[(rs * 2 + half_sel) * kcols + hs * a.hvn + vsel])[part];
-                    float2 f0 = unpack2(raw.x), f1 = unpack2(raw.y);
-                    const int h = head0 + hs;
-                    if (A.k_ref != nullptr) {
-                        const uint2 r = __ldg(reinterpret_cast<const uint2*>(A.k_ref) + h * 32 + lane);
-                        const float2 r0 = unpack2(r.x), r1 = unpack2(r.y);
-                        f0.x = __fsub_rn(f0.x, r0.x); f0.y = __fsub_rn(f0.y, r0.y);
-                        f1.x = __fsub_rn(f1.x, r1.x); f1.y = __fsub_rn(f1.y, r1.y);
-                    }
-                    v4[n][0] = f0.x; v4[n][1] = f0.y; v4[n][2] = f1.x; v4[n][3] = f1.y;
-                    const size_t at = cache_row(PAGED ? A.page_table : nullptr, cache_first + row0 + rs) * a.n_kv + h;
-                    dstp[n] = reinterpret_cast<uint8_t*>(A.k_cache) + at * BPV;
-                    metap[n] = A.k_meta + at;
-                    hk += step_h;
-                    rl += step_r;
-                    if (hk >= heads) { hk -= heads; rl++; }
+                for (int i = 0; i < 4; i++) {
+                    const float2 f0 = unpack2(w0[i] ^ flip[i]), f1 = unpack2(w1[i] ^ flip[4 + i]);
+                    v16[2 * i] = f0.x; v16[2 * i + 1] = f0.y;
+                    v16[8 + 2 * i] = f1.x; v16[8 + 2 * i + 1] = f1.y;
                 }
-                tq_store_vecs<FMT, kTqPair>(v4, lane, dstp, metap, livep, tq_cells);
+                if (A.k_ref != nullptr) {
+                    /* (x - ref) * sign == x * sign - ref * sign: the reference key gets the same flips */
+                    const vec16 r0 = __ldg(A.k_ref + h * 16 + 2 * sub), r1 = __ldg(A.k_ref + h * 16 + 2 * sub + 1);
+                    const uint32_t* q0 = reinterpret_cast<const uint32_t*>(&r0);
+                    const uint32_t* q1 = reinterpret_cast<const uint32_t*>(&r1);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float2 f0 = unpack2(q0[i] ^ flip[i]), f1 = unpack2(q1[i] ^ flip[4 + i]);
+                        v16[2 * i] = __fsub_rn(v16[2 * i], f0.x); v16[2 * i + 1] = __fsub_rn(v16[2 * i + 1], f0.y);
+                        v16[8 + 2 * i] = __fsub_rn(v16[8 + 2 * i], f1.x); v16[8 + 2 * i + 1] = __fsub_rn(v16[8 + 2 * i + 1], f1.y);
+                    }
+                }
+                const size_t at = cache_row(PAGED ? A.page_table : nullptr, cache_first + row0 + rs) * a.n_kv + h;
+                tq_store16<FMT>(v16, lane, reinterpret_cast<uint8_t*>(A.k_cache) + at * BPV, A.k_meta + at, live, tq_cells);
+                hk += step_h;
+                rl += step_r;
+                if (hk >= heads) { hk -= heads; rl++; }
             }
         }
     } else if (FMT != KV_RAW && staged) {

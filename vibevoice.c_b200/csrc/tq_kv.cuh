@@ -2,19 +2,20 @@
  * tq_kv.cuh -- the reference's TurboQuant encodings of the KV cache
  * (include/vibevoice/kv_quant.h:37-40: VV_KV_TQ4 = 3, TQ3 = 4, TQ2 = 5,
  * TQ1_5 = 6; the stored bits are defined by src/cuda/kv_quant.cu:40-121 and
- * src/cuda/kv_codec.cuh:42-62,133-163,232-291), one 128-wide head vector per
- * warp.
+ * src/cuda/kv_codec.cuh:42-62,133-163,232-291).
  *
  * A stored vector is its randomized Hadamard transform, quantized against its
  * own RMS:
  *   v[d]  = value - reference key (float), times a fixed +-1 hashed from d;
- *   v     = WHT128(v) / sqrt(128): lane L of the warp holds v[4L .. 4L+3], two
- *           butterfly stages run inside the lane and five across lanes;
+ *   v     = WHT128(v) / sqrt(128): in the reference a warp holds a vector, lane L
+ *           the values v[4L .. 4L+3], two butterfly stages in the lane and five across
+ *           lanes; the store below gives a vector to eight lanes instead (the stages
+ *           pair the same values whoever holds them, so the bits are the same);
  *   sigma = sqrt(max(sum(v^2) / 128, 1e-12)), kept as FP16 beside the codes;
  *   code  = per value, how many of the format's decision thresholds
  *           v / sigma exceeds (4 / 3 / 2 bits); the 1.5-bit format codes pairs
  *           by the nearest of eight 2-D code words (3 bits a pair);
- *   lane L's codes are bits [nb*L, nb*(L+1)) of the vector, little endian.
+ *   the codes of values 4L .. 4L+3 are bits [nb*L, nb*(L+1)) of the vector, little endian.
  *
  * The reference builds with fast-math, so its square root, its 1 / sigma (which
  * the compiler turns into a reciprocal square root of the mean square) and its
@@ -262,77 +263,108 @@ __device__ __forceinline__ uint32_t tq_pack4(const float (&y)[4], float inv_sigm
     return bits;
 }
 
-/* NV head vectors, a warp, worked on side by side (the stages of one vector are a chain of
- * shuffles; two or four chains in flight hide each other's latency): lane holds the four
- * values x[4*lane ..] of each (already minus the reference key). Writes bytes_per_vec bytes
- * at dst[n] (2-byte aligned) and the FP16 sigma at meta[n] for every n with live[n]
- * (warp-uniform). `cells`: the CTA's filled cell table (4-bit format). Every lane
- * of the warp must call. */
-template <int FMT, int NV>
-__device__ __forceinline__ void tq_store_vecs(float (&v)[NV][4], int lane, uint8_t* const (&dst)[NV],
-                                              __half* const (&meta)[NV], const bool (&live)[NV],
-                                              const TqCells* cells) {
-    constexpr int NB = TqBits<FMT>::N;
-    /* the signs of values 4 lane .. 4 lane + 3 out of the compile-time bit pattern */
+/* ---- the store: EIGHT lanes to a vector, 16 consecutive values each ---------------------
+ * (The 32-lane form above, four values a lane, is the reference kernel's own distribution and
+ * is what the one-vector-per-warp rotation kernel for small inputs uses.) A butterfly stage computes (lo + hi, lo - hi) for the pairs (d, d + stride) whoever holds
+ * them, so any distribution of a vector over lanes gives the same bits; with 16 values in a
+ * lane four stages run there and only three cross lanes, and everything that is per vector
+ * (addresses, the RMS, its square roots) is paid by 8 lanes instead of 32. A warp works on
+ * four vectors at once (lane >> 3 says which); `sub` = lane & 7 is the place in the vector. */
+
+/* FP16 sign masks for values 16 sub .. 16 sub + 15, two values per word: flipping the sign
+ * bit of the half commutes with every rounding that follows, so it stands for the
+ * multiplication by +-1. */
+__device__ __forceinline__ void tq_flips16(int sub, uint32_t (&flip)[8]) {
     constexpr uint32_t s0 = tq_sign_word(0), s1 = tq_sign_word(1), s2 = tq_sign_word(2), s3 = tq_sign_word(3);
-    const uint32_t word = (lane & 16) ? ((lane & 8) ? s3 : s2) : ((lane & 8) ? s1 : s0);
-    const uint32_t mine = word >> (4 * (lane & 7));
-    float sgn[4];
+    const uint32_t word = (sub & 4) ? ((sub & 2) ? s3 : s2) : ((sub & 2) ? s1 : s0);
+    const uint32_t mine = (sub & 1) ? (word >> 16) : word;      /* low 16 bits: this lane's values */
 #pragma unroll
-    for (int i = 0; i < 4; i++) sgn[i] = ((mine >> i) & 1u) ? -1.0f : 1.0f;
+    for (int w = 0; w < 8; w++)
+        flip[w] = ((mine << (15 - 2 * w)) & 0x8000u) | ((mine << (30 - 2 * w)) & 0x80000000u);
+}
+
+/* stages of stride 1..8 in the lane, 16..64 against lanes ^1, ^2, ^4 */
+__device__ __forceinline__ void tq_wht128_16(float (&v)[16], int lane) {
 #pragma unroll
-    for (int n = 0; n < NV; n++)
+    for (int s = 1; s < 16; s <<= 1)
 #pragma unroll
-        for (int i = 0; i < 4; i++) v[n][i] = __fmul_rn(v[n][i], sgn[i]);
-    tq_wht128<NV>(v, lane);
-    float ss[NV];
+        for (int d = 0; d < 16; d++)
+            if (!(d & s)) {
+                const float lo = v[d], hi = v[d + s];
+                v[d] = __fadd_rn(lo, hi);
+                v[d + s] = __fsub_rn(lo, hi);
+            }
 #pragma unroll
-    for (int n = 0; n < NV; n++) {
-        ss[n] = 0.0f;
+    for (int m = 1; m < 8; m <<= 1) {
+        const float own = (lane & m) ? -1.0f : 1.0f;
+        float o[16];
+#pragma unroll
+        for (int d = 0; d < 16; d++) o[d] = __shfl_xor_sync(0xffffffffu, v[d], m);
+#pragma unroll
+        for (int d = 0; d < 16; d++) v[d] = __fmaf_rn(v[d], own, o[d]);     /* other -+ own, one rounding */
+    }
+}
+
+/* v: this lane's 16 values of its group's vector, sign flips already applied (and the
+ * reference key subtracted). Writes the lane's share of the codes at dst (the vector's first
+ * byte; 2-byte aligned) and, from the group's first lane, the FP16 RMS at meta, when `live`
+ * (uniform over the group of eight). Every lane of the warp must call. */
+template <int FMT>
+__device__ __forceinline__ void tq_store16(float (&v)[16], int lane, uint8_t* dst, __half* meta, bool live,
+                                           const TqCells* cells) {
+    constexpr int NB = TqBits<FMT>::N;                  /* bits of four values */
+    const int sub = lane & 7;
+    tq_wht128_16(v, lane);
+    /* sum of squares in the association of the 32-lane form: partial sums over runs of four
+     * values (what a lane holds there), then the halving tree over the run index 4 sub + j from
+     * its top bit down: bits 4, 3, 2 cross lanes (sub ^ 4, 2, 1), bits 1, 0 stay in the lane */
+    float part[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        part[j] = 0.0f;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            v[n][i] = __fmul_rn(v[n][i], kTqWhtNorm);
-            ss[n] = __fmaf_rn(v[n][i], v[n][i], ss[n]);
+            v[4 * j + i] = __fmul_rn(v[4 * j + i], kTqWhtNorm);
+            part[j] = __fmaf_rn(v[4 * j + i], v[4 * j + i], part[j]);
         }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
+    for (int m = 4; m > 0; m >>= 1)
 #pragma unroll
-        for (int n = 0; n < NV; n++) ss[n] = __fadd_rn(ss[n], __shfl_xor_sync(0xffffffffu, ss[n], o));
+        for (int j = 0; j < 4; j++) part[j] = __fadd_rn(part[j], __shfl_xor_sync(0xffffffffu, part[j], m));
+    const float ss = __fadd_rn(__fadd_rn(part[0], part[2]), __fadd_rn(part[1], part[3]));
+    const float mean_sq = fmaxf(tq_div_approx(ss, 128.0f), 1e-12f);
+    const float sigma = tq_sqrt_approx(mean_sq);
+    /* sigma (stored) is the approximate square root of the mean square; the scale the codes are
+     * taken against is the approximate RECIPROCAL square root of that same mean -- what the
+     * reference's fast-math build makes of 1.0f / sigma -- not a reciprocal of sigma: the two
+     * differ in the last bit often enough to move a code once in some 10^4 vectors. */
+    const float inv = tq_rsqrt_approx(mean_sq);
+    uint32_t bits[4];
 #pragma unroll
-    for (int n = 0; n < NV; n++) {
-        /* sigma (stored) is the approximate square root of the mean square; the scale the codes
-         * are taken against is the approximate RECIPROCAL square root of that same mean -- what the
-         * reference's fast-math build makes of 1.0f / sigma -- not a reciprocal of sigma: the two
-         * differ in the last bit often enough to move a code once in some 10^4 vectors. */
-        const float mean_sq = fmaxf(tq_div_approx(ss[n], 128.0f), 1e-12f);
-        const float sigma = tq_sqrt_approx(mean_sq);
-        const uint32_t bits = tq_pack4<FMT>(v[n], tq_rsqrt_approx(mean_sq), cells);
-
-        /* Lane L's NB bits are bits [NB * L, NB * (L + 1)) of the vector. 16 and 8 bits are a
-         * lane's own aligned store; 12 and 6 bits are put together over lane pairs / quads into
-         * three whole bytes, which the first lanes of the group store one byte each. The warp's
-         * stores cover one contiguous run of bytes_per_vec bytes. */
-        if constexpr (NB == 16) {
-            if (live[n]) reinterpret_cast<uint16_t*>(dst[n])[lane] = (uint16_t)bits;
-        } else if constexpr (NB == 8) {
-            if (live[n]) dst[n][lane] = (uint8_t)bits;
-        } else if constexpr (NB == 12) {
-            const uint32_t other = __shfl_xor_sync(0xffffffffu, bits, 1);
-            const uint32_t three = (lane & 1) ? (other | (bits << 12)) : (bits | (other << 12));
-            if (live[n]) {
-                uint8_t* at = dst[n] + 3 * (lane >> 1);
-                if (lane & 1) at[2] = (uint8_t)(three >> 16);
-                else { at[0] = (uint8_t)three; at[1] = (uint8_t)(three >> 8); }
-            }
-        } else {
-            uint32_t three = bits << (6 * (lane & 3));
-            three |= __shfl_xor_sync(0xffffffffu, three, 1);
-            three |= __shfl_xor_sync(0xffffffffu, three, 2);
-            if (live[n] && (lane & 3) != 3) dst[n][3 * (lane >> 2) + (lane & 3)] = (uint8_t)(three >> (8 * (lane & 3)));
-        }
-        if (live[n] && lane == 0) *meta[n] = __float2half_rn(sigma);
+    for (int j = 0; j < 4; j++) {
+        const float y[4] = {v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]};
+        bits[j] = tq_pack4<FMT>(y, inv, cells);         /* NB bits: those of lane 4 sub + j of the 32-lane form */
     }
+    if (!live) return;
+    if constexpr (NB == 16) {
+        *reinterpret_cast<uint2*>(dst + 8 * sub) = make_uint2(bits[0] | (bits[1] << 16), bits[2] | (bits[3] << 16));
+    } else if constexpr (NB == 8) {
+        *reinterpret_cast<uint32_t*>(dst + 4 * sub) = bits[0] | (bits[1] << 8) | (bits[2] << 16) | (bits[3] << 24);
+    } else if constexpr (NB == 12) {
+        uint16_t* d16 = reinterpret_cast<uint16_t*>(dst + 6 * sub);
+        const uint32_t lo = bits[0] | (bits[1] << 12) | (bits[2] << 24);        /* bits 0..31 of the lane's 48 */
+        d16[0] = (uint16_t)lo;
+        d16[1] = (uint16_t)(lo >> 16);
+        d16[2] = (uint16_t)((bits[2] >> 8) | (bits[3] << 4));
+    } else {
+        const uint32_t all = bits[0] | (bits[1] << 6) | (bits[2] << 12) | (bits[3] << 18);
+        uint8_t* d8 = dst + 3 * sub;
+        d8[0] = (uint8_t)all;
+        d8[1] = (uint8_t)(all >> 8);
+        d8[2] = (uint8_t)(all >> 16);
+    }
+    if (sub == 0) *meta = __float2half_rn(sigma);
 }
 
 }  // namespace vvb
